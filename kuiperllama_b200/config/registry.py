@@ -1,4 +1,4 @@
-"""One registry from an architecture's name (config.json ``architectures[0]``) to its
+"""One registry from an architecture's name (config.json ``architectures[0]``, or ``architecture``) to its
 typed configuration class.  KuiperLLama picks the model class in ``main`` and by build
 flags (demo/main.cpp:58, CMakeLists.txt:29-44); here the folder's config.json decides.
 """
@@ -42,8 +42,10 @@ def config_class(name: str) -> type:
 
 def config_from_dict(d: dict):
     archs = d.get("architectures")
+    if archs is None and isinstance(d.get("architecture"), str):      # some designs name one architecture, as a string
+        archs = [d["architecture"]]
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError('config.json needs "architectures": ["<name>"]')
+        raise ConfigError('config.json needs "architectures": ["<name>"] or "architecture": "<name>"')
     return config_class(archs[0]).from_dict(d)
 
 

@@ -36,10 +36,24 @@ class LayerSpec:
     prefix: str                      # tensor-name prefix, e.g. "model.layers.3."
     arrangement: str                 # registered block arrangement, e.g. "pre_norm"
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]
     mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    feed_forward_norm: Optional[PartSpec]
     position: Optional[PartSpec]     # position encoding handed to the mixer (None: none)
+    # What only some arrangements have ("sandwich"): a norm after each sublayer and a gate on its
+    # result.  ``feed_forward`` and ``feed_forward_norm`` may be None there (a layer of a mixer alone).
+    mixer_post_norm: Optional[PartSpec] = None
+    feed_forward_post_norm: Optional[PartSpec] = None
+    mixer_gate: Optional[PartSpec] = None
+    feed_forward_gate: Optional[PartSpec] = None
+
+    def parts(self):
+        """(family, attribute, spec) of every part the layer has, in the order they are built."""
+        out = [("norm", "mixer_norm", self.mixer_norm), ("mixer", "mixer", self.mixer),
+               ("norm", "feed_forward_norm", self.feed_forward_norm), ("feed_forward", "feed_forward", self.feed_forward),
+               ("norm", "mixer_post_norm", self.mixer_post_norm), ("norm", "feed_forward_post_norm", self.feed_forward_post_norm),
+               ("gate", "mixer_gate", self.mixer_gate), ("gate", "feed_forward_gate", self.feed_forward_gate)]
+        return [(f, a, s) for f, a, s in out if s is not None]
 
 
 @dataclass(frozen=True)

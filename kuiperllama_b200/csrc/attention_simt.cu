@@ -2,7 +2,7 @@
 //
 // This is the kernel of the true 32-bit path (prefill and decode) and the fallback of the
 // bfloat16 path for sizes and options that the tensor-core kernels refuse (a window, a
-// head size that is no multiple of 16 on their list).  One CTA of four warps per
+// head size that is not on their list; any head size up to 256 runs here).  One CTA of four warps per
 // (token, query head).  Query token t of slot s at position p reads keys lo..p of that
 // slot, lo = max(0, p - window + 1) with a window, else 0.  Head h reads kv head
 // h / (H / KV); score = (q . k) * scale; softmax with the maximum subtracted; o = sum p v
@@ -22,8 +22,17 @@ constexpr int ATT_MAX_PER_LANE = 8;      // head_dim <= 256
 template <typename T>
 __device__ __forceinline__ float dot_row(const T* __restrict__ k, const float* __restrict__ q, int hd);
 
+// Head sizes whose rows do not start on 16-byte boundaries take the element-by-element form.
+template <typename T>
+__device__ __forceinline__ float dot_row_scalar(const T* __restrict__ k, const float* __restrict__ q, int hd) {
+    float s = 0.f;
+    for (int i = 0; i < hd; ++i) s += to_f32(k[i]) * q[i];
+    return s;
+}
+
 template <>
 __device__ __forceinline__ float dot_row<float>(const float* __restrict__ k, const float* __restrict__ q, int hd) {
+    if (hd & 3) return dot_row_scalar(k, q, hd);
     float s = 0.f;
     for (int i = 0; i < hd; i += 4) {
         const float4 kv = *reinterpret_cast<const float4*>(k + i);
@@ -33,6 +42,7 @@ __device__ __forceinline__ float dot_row<float>(const float* __restrict__ k, con
 }
 template <>
 __device__ __forceinline__ float dot_row<bf16>(const bf16* __restrict__ k, const float* __restrict__ q, int hd) {
+    if (hd & 7) return dot_row_scalar(k, q, hd);
     float s = 0.f;
     for (int i = 0; i < hd; i += 8) {
         const uint4 raw = *reinterpret_cast<const uint4*>(k + i);
@@ -142,7 +152,7 @@ KL_API int kl_attention_simt(const void* q, int q_stride, void* out, const void*
                              const int* token_slot, int n_tokens, int H, int KV, int hd, float scale, int window,
                              int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return KL_OK;
-    if (hd % 16 || hd > 32 * ATT_MAX_PER_LANE || hd <= 0 || KV <= 0 || H % KV) return KL_ERR_BAD_SIZE;
+    if (hd > 32 * ATT_MAX_PER_LANE || hd <= 0 || KV <= 0 || H % KV) return KL_ERR_BAD_SIZE;
     if (H > 65535) return KL_ERR_BAD_SIZE;
     const dim3 grid(n_tokens, H);
     const size_t smem = (size_t)(hd + 2 * ATT_WARPS + ATT_WARPS * hd) * sizeof(float);

@@ -26,6 +26,9 @@ CSRC = os.path.dirname(os.path.abspath(__file__))
 # module name -> source file.  Headers every module depends on are listed in HEADERS.
 SOURCES: Dict[str, str] = {
     "rowwise": "rowwise.cu",
+    "norms": "norms.cu",
+    "elementwise": "elementwise.cu",
+    "recurrent": "recurrent.cu",
     "rope_kv": "rope_kv.cu",
     "attention_simt": "attention_simt.cu",
     "attention_decode": "attention_decode.cu",

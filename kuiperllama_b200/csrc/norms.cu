@@ -1,0 +1,163 @@
+// Norms around a float32 residual stream, with what a sandwich of norms needs folded in.
+//
+// One kernel does, for a row s of the step,
+//
+//     d = delta[s]                                  (the sublayer's result, compute dtype)
+//     d = d * sigmoid(gate[s] + gate_bias)          (a gated residual, if a gate is given)
+//     d = norm_post(d)                              (a norm after the sublayer, if one is given)
+//     x = residual[s] + d;  residual[s] = x         (32-bit sum, written back)
+//     out[r] = norm(x)                              (the norm before the next sublayer, if out is given)
+//
+// so that a block whose sublayers are normed before and after costs one row-wise kernel per
+// sublayer, as the pre-norm block's add_rmsnorm does.  Each norm is a layer norm
+// ((x - mean) / sqrt(mean((x - mean)^2) + eps) * w + b, the variance from the deviations, not
+// from E[x^2] - mean^2) or an RMS norm (x / sqrt(mean(x^2) + eps) * w).  All statistics, the
+// sigmoid and the sum are 32-bit.  ExiledOfCode/KuiperLLama has the RMS norm alone
+// (rmsnorm_kernel.cu:70-106) and its add as a kernel of its own (add_kernel.cu:4-12).
+//
+// A second kernel is the per-head RMS norm with an output gate that linear-attention mixers
+// end with: out[t, h, :] = x[t, h, :] / rms(x[t, h, :]) * w * silu(gate[t, h, :]).
+#include "common.cuh"
+
+namespace kl {
+
+enum : int { NORM_LAYER = 0, NORM_RMS = 1 };
+
+// Normalise buf[0..n) in place (shared memory, every thread strides over it).
+__device__ __forceinline__ void norm_in_place(float* buf, int n, const float* __restrict__ w, const float* __restrict__ b,
+                                              float eps, int kind, float* scratch) {
+    float mean = 0.f;
+    if (kind == NORM_LAYER) {
+        float s = 0.f;
+        for (int i = threadIdx.x; i < n; i += blockDim.x) s += buf[i];
+        mean = block_sum(s, scratch) / (float)n;
+    }
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) { const float d = buf[i] - mean; ss += d * d; }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        float y = (buf[i] - mean) * inv * w[i];
+        if (b != nullptr) y += b[i];
+        buf[i] = y;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+norm_chain_kernel(float* __restrict__ residual, const T* __restrict__ delta, long long delta_ld,
+                  const T* __restrict__ gate, long long gate_ld, const float* __restrict__ gate_bias,
+                  const float* __restrict__ post_w, const float* __restrict__ post_b, float post_eps, int post_kind,
+                  const float* __restrict__ w, const float* __restrict__ b, float eps, int kind,
+                  T* __restrict__ out, const int* __restrict__ rows, int hidden) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float smem[];
+    float* buf = smem;                 // [hidden]
+    float* scratch = smem + hidden;    // [33]
+    const int r = blockIdx.x;
+    const int s = rows ? rows[r] : r;
+    float* x = residual + (size_t)s * hidden;
+    if (delta != nullptr) {
+        const T* d = delta + (size_t)s * delta_ld;
+        const T* g = gate ? gate + (size_t)s * gate_ld : nullptr;
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            float v = to_f32(d[i]);
+            if (g != nullptr) {
+                const float a = to_f32(g[i]) + (gate_bias ? gate_bias[i] : 0.f);
+                v *= 1.0f / (1.0f + expf(-a));
+            }
+            buf[i] = v;
+        }
+        if (post_w != nullptr) {
+            __syncthreads();
+            norm_in_place(buf, hidden, post_w, post_b, post_eps, post_kind, scratch);
+        }
+        // every thread touches the same indices in each pass, so its own elements need no barrier here
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            const float v = x[i] + buf[i];
+            buf[i] = v;
+            if (rows == nullptr) x[i] = v;
+        }
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) buf[i] = x[i];
+    }
+    if (out == nullptr) return;
+    __syncthreads();
+    norm_in_place(buf, hidden, w, b, eps, kind, scratch);
+    T* o = out + (size_t)r * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_f32<T>(buf[i]);
+}
+
+// x: float32 [tokens, heads * dim]; gate: compute dtype, row stride gate_ld, same columns;
+// w: float32 [dim] shared by the heads (or null).  One warp per (token, head).
+template <typename T>
+__global__ void __launch_bounds__(128)
+head_rmsnorm_gate_kernel(const float* __restrict__ x, const T* __restrict__ gate, long long gate_ld, const float* __restrict__ w,
+                         T* __restrict__ out, int tokens, int heads, int dim, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= (long long)tokens * heads) return;
+    const int t = (int)(item / heads), h = (int)(item - (long long)t * heads);
+    const float* xr = x + ((size_t)t * heads + h) * dim;
+    float ss = 0.f;
+    for (int i = lane; i < dim; i += 32) ss += xr[i] * xr[i];
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+    const T* g = gate ? gate + (size_t)t * gate_ld + (size_t)h * dim : nullptr;
+    T* o = out + ((size_t)t * heads + h) * dim;
+    for (int i = lane; i < dim; i += 32) {
+        float y = xr[i] * inv;
+        if (w != nullptr) y *= w[i];
+        if (g != nullptr) { const float a = to_f32(g[i]); y *= a / (1.0f + expf(-a)); }
+        o[i] = from_f32<T>(y);
+    }
+}
+
+}  // namespace kl
+
+using namespace kl;
+
+// delta, gate, out: compute dtype (`dtype`); everything else float32.  Null pointers switch steps off:
+// no delta (nothing is added), no gate, no post norm (post_w null), no output (out null: only the sum).
+KL_API int kl_norm_chain(float* residual, const void* delta, long long delta_ld, const void* gate, long long gate_ld,
+                         const float* gate_bias, const float* post_w, const float* post_b, float post_eps, int post_kind,
+                         const float* w, const float* b, float eps, int kind, void* out, const int* rows, int n_rows,
+                         int hidden, int dtype, cudaStream_t stream) {
+    if (n_rows <= 0) return KL_OK;
+    if (hidden <= 0 || (out != nullptr && w == nullptr)) return KL_ERR_BAD_SIZE;
+    if ((kind != NORM_LAYER && kind != NORM_RMS) || (post_kind != NORM_LAYER && post_kind != NORM_RMS)) return KL_ERR_BAD_SIZE;
+    const size_t smem = (size_t)(hidden + 33) * sizeof(float);
+    if (smem > 200 * 1024) return KL_ERR_BAD_SIZE;
+    const int threads = hidden >= 1024 ? 256 : 128;
+#define KL_CHAIN(T)                                                                                                        \
+    do {                                                                                                                   \
+        if (smem > 48 * 1024) KL_CUDA(cudaFuncSetAttribute(norm_chain_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        launch_kernel(norm_chain_kernel<T>, n_rows, threads, smem, stream, residual, (const T*)delta, delta_ld, (const T*)gate, gate_ld, \
+                      gate_bias, post_w, post_b, post_eps, post_kind, w, b, eps, kind, (T*)out, rows, hidden);                \
+    } while (0)
+    if (dtype == KL_F32) KL_CHAIN(float);
+    else if (dtype == KL_BF16) KL_CHAIN(bf16);
+    else return KL_ERR_BAD_DTYPE;
+#undef KL_CHAIN
+    KL_LAUNCH_CHECK();
+    return KL_OK;
+}
+
+KL_API int kl_head_rmsnorm_gate(const float* x, const void* gate, long long gate_ld, const float* w, void* out, int tokens,
+                                int heads, int dim, float eps, int dtype, cudaStream_t stream) {
+    if (tokens <= 0 || heads <= 0) return KL_OK;
+    if (dim <= 0) return KL_ERR_BAD_SIZE;
+    const long long items = (long long)tokens * heads;
+    const int blocks = (int)((items + 3) / 4);
+    if (dtype == KL_F32)
+        launch_kernel(head_rmsnorm_gate_kernel<float>, blocks, 128, 0, stream, x, (const float*)gate, gate_ld, w, (float*)out, tokens, heads, dim, eps);
+    else if (dtype == KL_BF16)
+        launch_kernel(head_rmsnorm_gate_kernel<bf16>, blocks, 128, 0, stream, x, (const bf16*)gate, gate_ld, w, (bf16*)out, tokens, heads, dim, eps);
+    else
+        return KL_ERR_BAD_DTYPE;
+    KL_LAUNCH_CHECK();
+    return KL_OK;
+}

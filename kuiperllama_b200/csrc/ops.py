@@ -170,17 +170,147 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
            "swiglu")
 
 
+# --------------------------------------------------------------------------- norm chains, activations, gates
+
+NORM_KINDS = {"layernorm": 0, "rmsnorm": 1}
+ACTIVATIONS = {"xielu": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def _columns(t: Optional[torch.Tensor], n: int, width: int, name: str) -> None:
+    """``t`` is [>= n, width] with unit column stride (rows may be a stacked product's column slice)."""
+    if t is not None:
+        _need(t.dim() == 2 and t.shape[0] >= n and t.shape[1] == width and t.stride(1) == 1, f"{name}: expected [{n}, {width}] rows")
+
+
+def norm_chain(residual: torch.Tensor, delta: Optional[torch.Tensor], out: Optional[torch.Tensor], weight: Optional[torch.Tensor],
+               bias: Optional[torch.Tensor], eps: float, kind: str, gate: Optional[torch.Tensor] = None,
+               gate_bias: Optional[torch.Tensor] = None, post: Optional[tuple] = None, rows: Optional[torch.Tensor] = None,
+               dtype: Optional[torch.dtype] = None) -> None:
+    """d = delta * sigmoid(gate + gate_bias); d = post-norm(d); x = residual + d (written back unless
+    ``rows``); out = norm(x).  Every step but the last is optional: ``delta`` None adds nothing,
+    ``post`` = (weight, bias or None, eps, kind) or None, ``out`` None only updates the stream.
+    ``delta`` and ``gate`` are [n, hidden] in the compute dtype with any row stride."""
+    _cuda(residual, delta, out, weight, bias, gate, gate_bias, rows)
+    _i32(rows, "rows")
+    hidden = residual.shape[-1]
+    n = rows.numel() if rows is not None else residual.shape[0]
+    _need(residual.dtype == torch.float32 and residual.is_contiguous(), "norm_chain: the residual stream is float32")
+    if dtype is None:
+        dtype = out.dtype if out is not None else delta.dtype
+    for t, nm in ((delta, "delta"), (gate, "gate")):
+        if t is not None:
+            _need(t.dtype == dtype and t.dim() == 2 and t.shape[1] == hidden and t.stride(1) == 1 and t.shape[0] >= residual.shape[0],
+                  f"norm_chain: {nm} must be [rows, hidden] in the compute dtype")
+    _need(gate is None or delta is not None, "norm_chain: a gate needs something to gate")
+    for t in (weight, bias, gate_bias) + (tuple(post[:2]) if post is not None else ()):
+        _need(t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == hidden), "norm_chain: float32 [hidden] vectors")
+    if out is not None:
+        _need(out.is_contiguous() and out.dtype == dtype and out.shape[-1] == hidden and out.shape[0] >= n and weight is not None,
+              "norm_chain: output shape")
+    pw, pb, peps, pkind = post if post is not None else (None, None, 0.0, kind)
+    _check(lib("norms").kl_norm_chain(
+        _ptr(residual), _ptr(delta), ctypes.c_longlong(delta.stride(0) if delta is not None else 0), _ptr(gate),
+        ctypes.c_longlong(gate.stride(0) if gate is not None else 0), _ptr(gate_bias), _ptr(pw), _ptr(pb), ctypes.c_float(peps),
+        NORM_KINDS[pkind], _ptr(weight), _ptr(bias), ctypes.c_float(eps), NORM_KINDS[kind], _ptr(out), _ptr(rows), n, hidden,
+        dtype_code(dtype), _stream()), "norm_chain")
+
+
+def head_rmsnorm_gate(x: torch.Tensor, gate: Optional[torch.Tensor], weight: Optional[torch.Tensor], out: torch.Tensor,
+                      heads: int, dim: int, eps: float) -> None:
+    """out[t, h, :] = x[t, h, :] / sqrt(mean(x[t, h, :]^2) + eps) * weight * silu(gate[t, h, :]); x float32
+    [tokens, heads * dim], gate (compute dtype, any row stride) and weight (float32 [dim]) optional."""
+    _cuda(x, gate, weight, out)
+    n = x.shape[0]
+    _need(x.dtype == torch.float32 and x.is_contiguous() and x.shape[1] == heads * dim, "head_rmsnorm_gate: x")
+    _need(out.is_contiguous() and tuple(out.shape) == (n, heads * dim), "head_rmsnorm_gate: out")
+    _columns(gate, n, heads * dim, "head_rmsnorm_gate: gate")
+    _need(gate is None or gate.dtype == out.dtype, "head_rmsnorm_gate: gate dtype")
+    _need(weight is None or (weight.dtype == torch.float32 and weight.numel() == dim and weight.is_contiguous()), "head_rmsnorm_gate: weight")
+    _check(lib("norms").kl_head_rmsnorm_gate(_ptr(x), _ptr(gate), ctypes.c_longlong(gate.stride(0) if gate is not None else 0),
+                                             _ptr(weight), _ptr(out), n, heads, dim, ctypes.c_float(eps), dtype_code(out.dtype),
+                                             _stream()), "head_rmsnorm_gate")
+
+
+def activation(x: torch.Tensor, out: torch.Tensor, kind: str, params: Optional[torch.Tensor] = None) -> None:
+    """out = act(x) element by element; ``kind`` in ACTIVATIONS.  "xielu" takes ``params`` = float32
+    [softplus(p), 1/2 + softplus(q)]: a z^2 + z / 2 above zero, b (exp(z) - 1 - z) + z / 2 below."""
+    _cuda(x, out, params)
+    n, width = x.shape
+    _columns(x, n, width, "activation: x"); _columns(out, n, width, "activation: out")
+    _need(x.dtype == out.dtype, "activation: dtypes differ")
+    _need(params is None or (params.dtype == torch.float32 and params.numel() >= 2 and params.is_contiguous()), "activation: params")
+    _check(lib("elementwise").kl_activation(_ptr(x), ctypes.c_longlong(x.stride(0)), _ptr(out), ctypes.c_longlong(out.stride(0)), n, width,
+                                            ACTIVATIONS[kind], _ptr(params), dtype_code(x.dtype), _stream()), "activation")
+
+
+def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor) -> None:
+    """x *= sigmoid(gate) in place; both [tokens, width] in the compute dtype, any row stride."""
+    _cuda(x, gate)
+    n, width = x.shape
+    _columns(x, n, width, "sigmoid_gate: x"); _columns(gate, n, width, "sigmoid_gate: gate")
+    _need(x.dtype == gate.dtype, "sigmoid_gate: dtypes differ")
+    _check(lib("elementwise").kl_sigmoid_gate(_ptr(x), ctypes.c_longlong(x.stride(0)), _ptr(gate), ctypes.c_longlong(gate.stride(0)),
+                                              n, width, dtype_code(x.dtype), _stream()), "sigmoid_gate")
+
+
+# --------------------------------------------------------------------------- recurrent mixers
+
+def mingru_scan(proj: torch.Tensor, z_col: int, x_col: int, g_col: int, bias_z: Optional[torch.Tensor], bias_x: Optional[torch.Tensor],
+                state: torch.Tensor, out: torch.Tensor, step, width: int) -> None:
+    """The minGRU recurrence over a ragged step.  ``proj`` [rows, >= 3 width] holds the z, x and gate
+    projections at the given columns; ``state`` float32 [slots, width] is read and left updated."""
+    _cuda(proj, bias_z, bias_x, state, out)
+    _need(proj.dim() == 2 and proj.stride(1) == 1 and max(z_col, x_col, g_col) + width <= proj.shape[1], "mingru_scan: projections")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.shape[1] == width and state.stride(1) == 1, "mingru_scan: state")
+    _need(out.is_contiguous() and out.dtype == proj.dtype and out.shape[1] == width and out.shape[0] >= step.n_tokens, "mingru_scan: out")
+    for b in (bias_z, bias_x):
+        _need(b is None or (b.dtype == torch.float32 and b.numel() == width and b.is_contiguous()), "mingru_scan: bias")
+    _check(lib("recurrent").kl_mingru_scan(_ptr(proj), ctypes.c_longlong(proj.stride(0)), z_col, x_col, g_col, _ptr(bias_z), _ptr(bias_x),
+                                           _ptr(state), ctypes.c_longlong(state.stride(0)), _ptr(out), _ptr(step.cu_tokens),
+                                           _ptr(step.seq_slots), step.n_seqs, width, dtype_code(proj.dtype), _stream()), "mingru_scan")
+
+
+def gated_delta_rule(proj: torch.Tensor, conv_col: int, b_col: int, a_col: int, conv_weight: torch.Tensor, A_log: torch.Tensor,
+                     dt_bias: torch.Tensor, state: torch.Tensor, conv_off: int, out: torch.Tensor, step, heads: int, kv_heads: int,
+                     dim: int, vdim: int, q_scale: float, unit_eps: float) -> None:
+    """The gated delta rule over a ragged step (see recurrent.cu).  ``proj`` holds q | k | v at
+    ``conv_col`` and the projections of beta and of the decay at ``b_col`` and ``a_col``;
+    ``conv_weight`` float32 [2 G d + H dv, taps]; ``state`` float32 [slots, S | convolution state];
+    ``out`` float32 [rows, H * dv]."""
+    _cuda(proj, conv_weight, A_log, dt_bias, state, out)
+    C = 2 * kv_heads * dim + heads * vdim
+    taps = conv_weight.shape[1]
+    n = step.n_tokens
+    _need(proj.dim() == 2 and proj.stride(1) == 1 and conv_col + C <= proj.shape[1] and max(b_col, a_col) + heads <= proj.shape[1],
+          "gated_delta_rule: projections")
+    _need(conv_weight.dtype == torch.float32 and conv_weight.is_contiguous() and conv_weight.shape[0] == C, "gated_delta_rule: taps")
+    _need(all(t.dtype == torch.float32 and t.numel() == heads and t.is_contiguous() for t in (A_log, dt_bias)), "gated_delta_rule: per-head vectors")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1
+          and state.shape[1] >= conv_off + (taps - 1) * C and conv_off >= heads * vdim * dim, "gated_delta_rule: state")
+    _need(out.dtype == torch.float32 and out.is_contiguous() and out.shape[0] >= n and out.shape[1] == heads * vdim, "gated_delta_rule: out")
+    _need(dim <= 256, f"gated_delta_rule: key size {dim} is above 256")
+    prep = torch.empty((n, C), dtype=torch.float32, device=proj.device)
+    bg = torch.empty((n, 2 * heads), dtype=torch.float32, device=proj.device)
+    _check(lib("recurrent").kl_gated_delta_rule(
+        _ptr(proj), ctypes.c_longlong(proj.stride(0)), conv_col, b_col, a_col, _ptr(conv_weight), taps, _ptr(A_log), _ptr(dt_bias),
+        _ptr(state), ctypes.c_longlong(state.stride(0)), ctypes.c_longlong(conv_off), _ptr(prep), _ptr(bg), _ptr(out),
+        _ptr(step.cu_tokens), _ptr(step.seq_slots), step.n_seqs, step.max_new, heads, kv_heads, dim, vdim, ctypes.c_float(q_scale),
+        ctypes.c_float(unit_eps), dtype_code(proj.dtype), _stream()), "gated_delta_rule", 2)
+
+
 # --------------------------------------------------------------------------- position encoding + cache write
 
 def rope_kv_write(qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], rotary_dim: int, positions: torch.Tensor,
                   token_slot: torch.Tensor, block_table: torch.Tensor, k_cache: Optional[torch.Tensor],
                   v_cache: Optional[torch.Tensor], num_heads: int, num_kv_heads: int, head_dim: int,
-                  partials: Optional[torch.Tensor] = None) -> None:
+                  partials: Optional[torch.Tensor] = None, values_are_keys: bool = False) -> None:
     """Rotate the query heads of ``qkv`` [tokens, (H + 2 KV) * hd] in place; rotate the key
     heads and store them, and the value heads, into the paged cache
     [pages, KV, PAGE, hd] (skipped when both caches are None).  With ``partials`` (float32
     [S, tokens, width]) the projections are the sum of those pieces and ``qkv`` only receives
-    the rotated queries."""
+    the rotated queries.  ``qkv`` may be wider than that (the leading columns of a stacked product
+    count).  With ``values_are_keys`` it holds no value heads: the key heads as they are, before
+    rotation, are stored as values."""
     _cuda(qkv, inv_freq, positions, token_slot, block_table, k_cache, v_cache, partials)
     n_parts, stride = 0, 0
     if partials is not None:
@@ -189,7 +319,9 @@ def rope_kv_write(qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], rotary_di
         n_parts, stride = partials.shape[0], partials.shape[1] * partials.shape[2]
     _i32(positions, "positions"); _i32(token_slot, "token_slot"); _i32(block_table, "block_table")
     n = qkv.shape[0]
-    _need(qkv.is_contiguous() and qkv.shape[1] == (num_heads + 2 * num_kv_heads) * head_dim, "rope_kv_write: qkv shape")
+    cols = (num_heads + (1 if values_are_keys else 2) * num_kv_heads) * head_dim
+    _need(qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] >= cols, "rope_kv_write: qkv shape")
+    _need(partials is None or (qkv.is_contiguous() and qkv.shape[1] == cols and not values_are_keys), "rope_kv_write: pieces need plain rows")
     _need(positions.numel() >= n and token_slot.numel() >= n, "rope_kv_write: one position and slot per token")
     write = k_cache is not None
     if write:
@@ -203,8 +335,8 @@ def rope_kv_write(qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], rotary_di
     _check(lib("rope_kv").kl_rope_kv_write(_ptr(qkv), _ptr(partials), n_parts, ctypes.c_longlong(stride),
                                            _ptr(inv_freq), rotary_dim, _ptr(positions), _ptr(token_slot),
                                            _ptr(block_table), block_table.shape[1], _ptr(k_cache), _ptr(v_cache), n,
-                                           num_heads, num_kv_heads, head_dim, int(write), dtype_code(qkv.dtype),
-                                           _stream()), "rope_kv_write")
+                                           num_heads, num_kv_heads, head_dim, int(write), ctypes.c_longlong(qkv.stride(0)),
+                                           int(values_are_keys), dtype_code(qkv.dtype), _stream()), "rope_kv_write")
 
 
 # --------------------------------------------------------------------------- attention
@@ -219,7 +351,7 @@ def attention_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: t
     _need(q.dtype == out.dtype == k_cache.dtype == v_cache.dtype, "attention: dtypes differ")
     _need(k_cache.is_contiguous() and v_cache.is_contiguous()
           and tuple(k_cache.shape[1:]) == (num_kv_heads, PAGE, head_dim), "attention: cache layout")
-    _need(head_dim % 16 == 0 and head_dim <= 256, f"attention: head_dim {head_dim} must be a multiple of 16 up to 256")
+    _need(0 < head_dim <= 256, f"attention: head_dim {head_dim} must be at most 256")
     _need(num_heads % num_kv_heads == 0, "attention: heads must be a multiple of kv heads")
     _check(lib("attention_simt").kl_attention_simt(_ptr(q), q_stride, _ptr(out), _ptr(k_cache), _ptr(v_cache),
                                                    _ptr(block_table), block_table.shape[1], _ptr(positions),
@@ -786,14 +918,15 @@ def attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.
             and q_stride % 8 == 0 and q.data_ptr() % 16 == 0 and step.max_new >= 8):
         attention_tcgen05(q, q_stride, out, k_cache, v_cache, block_table, step.cu_tokens, step.seq_slots, step.seq_starts,
                           step.seq_new, step.n_seqs, step.max_new, step.n_tokens, num_heads, num_kv_heads, head_dim, scale)
-    elif bf and head_dim in MMA_HEAD_DIMS and group <= 16 and (not step.is_decode or DECODE_KERNEL == "mma"):
+    elif (bf and head_dim in MMA_HEAD_DIMS and group <= 16 and (not step.is_decode or DECODE_KERNEL == "mma")
+          and q_stride % 2 == 0 and q.data_ptr() % 4 == 0):
         splits = 1
         if step.is_decode:
             splits = decode_attention_splits(step.n_seqs, num_kv_heads, head_dim, getattr(step, "context_class", 0))
         attention_mma(q, q_stride, out, k_cache, v_cache, block_table, step.cu_tokens, step.seq_slots, step.seq_starts,
                       step.seq_new, step.n_seqs, step.max_new, step.n_tokens, num_heads, num_kv_heads, head_dim, scale,
                       window, splits, few_rows=step.is_decode)
-    elif bf and step.is_decode and head_dim in DECODE_HEAD_DIMS and q_stride % 8 == 0:
+    elif bf and step.is_decode and head_dim in DECODE_HEAD_DIMS and q_stride % 8 == 0 and q.data_ptr() % 16 == 0:
         attention_decode(q, q_stride, out, k_cache, v_cache, block_table, step.positions, step.token_slot, step.n_tokens,
                          num_heads, num_kv_heads, head_dim, scale, window)
     else:

@@ -12,7 +12,9 @@
 
 namespace kl {
 
-// qkv: [tokens, (H + 2 KV) * hd], query heads first, then key heads, then value heads.
+// qkv: [tokens, (H + 2 KV) * hd], query heads first, then key heads, then value heads; rows may be
+// `row_stride` elements apart (the leading columns of a wider stacked product).  With `v_from_k` there
+// are no value heads: the values are the key heads as projected, before their rotation.
 // With n_partials > 0 the projections arrive as float32 partial sums
 // [n_partials][tokens][(H + 2 KV) * hd] of a product whose K range was cut: they are added in
 // ascending order here, rotated in float32, and qkv only receives the rotated queries.
@@ -22,7 +24,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
                                      const int* __restrict__ positions, const int* __restrict__ token_slot,
                                      const int* __restrict__ block_table, int blocks_per_seq,
                                      T* __restrict__ k_cache, T* __restrict__ v_cache,
-                                     int H, int KV, int hd, int write_kv) {
+                                     int H, int KV, int hd, int write_kv, long long row_stride, int v_from_k) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -30,7 +32,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
     if (slot < 0) return;                                   // a padding row
     const int pos = positions[t];
     const int width = (H + 2 * KV) * hd;
-    T* row = qkv + (size_t)t * width;
+    T* row = qkv + (size_t)t * row_stride;
+    const int v_src = v_from_k ? H * hd : (H + KV) * hd;       // first column of what is stored as values
     const float* prow = n_partials > 0 ? partials + (size_t)t * width : nullptr;
     auto value = [&](int idx) {                             // element idx of this token's q|k|v row, in float32
         if (prow == nullptr) return to_f32(row[idx]);
@@ -90,7 +93,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
                     const int idx = (w - n_qk8) << 3;
                     const int g = idx / hd, e = idx - g * hd;
                     T* dst = (T*)v_cache + cache_row_offset(block_table, blocks_per_seq, slot, pos, g, KV, hd);
-                    *reinterpret_cast<uint4*>(dst + e) = *reinterpret_cast<const uint4*>(row + (size_t)(H + KV) * hd + idx);
+                    *reinterpret_cast<uint4*>(dst + e) = *reinterpret_cast<const uint4*>(row + (size_t)v_src + idx);
                 }
             }
             return;
@@ -120,7 +123,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
                 const int idx = w - n_qk;
                 const int g = idx / hd, e = idx - g * hd;
                 T* dst = v_cache + cache_row_offset(block_table, blocks_per_seq, slot, pos, g, KV, hd);
-                dst[e] = from_f32<T>(value((H + KV) * hd + idx));
+                dst[e] = from_f32<T>(value(v_src + idx));
             }
         }
         return;
@@ -128,6 +131,14 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
     {
         // Partial or absent rotation (one CTA per token): pairs (j, j + rot/2) for j < rot/2; the
         // rest passes through.
+        if (write_kv && v_from_k) {                         // the values are the keys before they turn
+            for (int idx = threadIdx.x; idx < KV * hd; idx += blockDim.x) {
+                const int g = idx / hd, e = idx - g * hd;
+                T* dst = v_cache + cache_row_offset(block_table, blocks_per_seq, slot, pos, g, KV, hd);
+                dst[e] = row[(size_t)v_src + idx];
+            }
+            __syncthreads();
+        }
         const int n_pairs = (H + KV) * rhalf;
         for (int idx = threadIdx.x; idx < n_pairs; idx += blockDim.x) {
             const int head = idx / rhalf;
@@ -148,11 +159,11 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
             }
         }
     }
-    if (write_kv) {
+    if (write_kv && !v_from_k) {
         for (int idx = threadIdx.x; idx < KV * hd; idx += blockDim.x) {
             const int g = idx / hd, e = idx - g * hd;
             T* dst = v_cache + cache_row_offset(block_table, blocks_per_seq, slot, pos, g, KV, hd);
-            dst[e] = from_f32<T>(value((H + KV) * hd + idx));
+            dst[e] = from_f32<T>(value(v_src + idx));
         }
     }
 }
@@ -164,28 +175,30 @@ using namespace kl;
 KL_API int kl_rope_kv_write(void* qkv, const float* partials, int n_partials, long long partial_stride,
                             const float* inv_freq, int rotary_dim, const int* positions,
                             const int* token_slot, const int* block_table, int blocks_per_seq, void* k_cache,
-                            void* v_cache, int n_tokens, int H, int KV, int hd, int write_kv, int dtype,
-                            cudaStream_t stream) {
+                            void* v_cache, int n_tokens, int H, int KV, int hd, int write_kv, long long row_stride,
+                            int v_from_k, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return KL_OK;
     if (hd % 2 || rotary_dim % 2 || rotary_dim > hd || rotary_dim < 0) return KL_ERR_BAD_SIZE;
     if (rotary_dim > 0 && inv_freq == nullptr) return KL_ERR_BAD_SIZE;
     if (n_partials < 0 || (n_partials > 0 && partials == nullptr)) return KL_ERR_BAD_SIZE;
+    const int cols = (H + (v_from_k ? 1 : 2) * KV) * hd;
+    if (row_stride < cols || (n_partials > 0 && (v_from_k || row_stride != cols))) return KL_ERR_BAD_SIZE;
     const int work = (H + KV) * hd / 2 + (write_kv ? KV * hd : 0);
     const int threads = work >= 1024 ? 256 : (work >= 256 ? 128 : 64);
     // full rotation: a token's work is spread over several CTAs (one item per thread; rows of
     // bfloat16 without partial sums take eight items per thread)
     const bool vec = dtype == KL_BF16 && n_partials == 0 && rotary_dim == hd && (hd % 16) == 0 &&
-                     (((H + 2 * KV) * hd) % 8) == 0 && ((uintptr_t)qkv & 15) == 0;
+                     (row_stride % 8) == 0 && ((uintptr_t)qkv & 15) == 0;
     const int items = vec ? (work + 7) / 8 : work;
     const int ctas = rotary_dim == hd ? (items + threads - 1) / threads : 1;
     if (dtype == KL_F32)
         launch_kernel(rope_kv_write_kernel<float>, dim3(n_tokens, ctas), threads, 0, stream, (float*)qkv, partials, n_partials,
             (size_t)partial_stride, inv_freq, rotary_dim, positions,
-            token_slot, block_table, blocks_per_seq, (float*)k_cache, (float*)v_cache, H, KV, hd, write_kv);
+            token_slot, block_table, blocks_per_seq, (float*)k_cache, (float*)v_cache, H, KV, hd, write_kv, row_stride, v_from_k);
     else if (dtype == KL_BF16)
         launch_kernel(rope_kv_write_kernel<bf16>, dim3(n_tokens, ctas), threads, 0, stream, (bf16*)qkv, partials, n_partials,
             (size_t)partial_stride, inv_freq, rotary_dim, positions,
-            token_slot, block_table, blocks_per_seq, (bf16*)k_cache, (bf16*)v_cache, H, KV, hd, write_kv);
+            token_slot, block_table, blocks_per_seq, (bf16*)k_cache, (bf16*)v_cache, H, KV, hd, write_kv, row_stride, v_from_k);
     else
         return KL_ERR_BAD_DTYPE;
     KL_LAUNCH_CHECK();

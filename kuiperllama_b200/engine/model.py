@@ -15,8 +15,8 @@ import torch
 from ..cache import KVRequest, SequenceCache, StateRequest
 from ..config.spec import LayerSpec, ModelSpec
 from ..csrc import ops
-from ..parts.base import Runtime, StepContext, part_class
-from ..parts.linear import Linear
+from ..parts.base import Part, Runtime, StepContext, part_class
+from ..parts.linear import Linear, StackedInput
 from ..weights.loader import TensorDecl
 
 
@@ -24,8 +24,7 @@ def model_manifest(spec: ModelSpec) -> Dict[str, TensorDecl]:
     """Every tensor the model reads, gathered from its parts."""
     m: Dict[str, TensorDecl] = {spec.embedding_name: TensorDecl((spec.vocab_size, spec.hidden_size))}
     for layer in spec.layers:
-        for family, ps in (("norm", layer.mixer_norm), ("mixer", layer.mixer),
-                           ("norm", layer.feed_forward_norm), ("feed_forward", layer.feed_forward)):
+        for family, _, ps in layer.parts():
             m.update(part_class(family, ps.kind).manifest(ps, layer.prefix))
         if layer.position is not None:
             m.update(part_class("position", layer.position.kind).manifest(layer.position, layer.prefix))
@@ -67,11 +66,12 @@ class DecoderModel:
         position = None
         if layer.position is not None:
             position = part_class("position", layer.position.kind)(layer.position, layer.prefix, tensors, rt)
-        mixer = part_class("mixer", layer.mixer.kind)(layer.mixer, layer.prefix, tensors, rt, position)
-        ffn = part_class("feed_forward", layer.feed_forward.kind)(layer.feed_forward, layer.prefix, tensors, rt)
-        n1 = part_class("norm", layer.mixer_norm.kind)(layer.mixer_norm, layer.prefix, tensors, rt)
-        n2 = part_class("norm", layer.feed_forward_norm.kind)(layer.feed_forward_norm, layer.prefix, tensors, rt)
-        block = part_class("arrangement", layer.arrangement)(n1, mixer, n2, ffn)
+        built = {}
+        for family, attr, ps in layer.parts():
+            cls = part_class(family, ps.kind)
+            built[attr] = cls(ps, layer.prefix, tensors, rt, position) if family == "mixer" else cls(ps, layer.prefix, tensors, rt)
+        first = [built.pop(a, None) for a in ("mixer_norm", "mixer", "feed_forward_norm", "feed_forward")]
+        block = part_class("arrangement", layer.arrangement)(*first, **built)     # what is left: parts only some arrangements take
         block.position = position
         return block
 
@@ -145,9 +145,16 @@ class DecoderModel:
         yield self.embedding
         yield self.lm_head.weight
         for b in self.blocks:
-            for part in (b.mixer_norm, b.mixer, b.feed_forward_norm, b.feed_forward):
+            for part in vars(b).values():
+                if not isinstance(part, Part):
+                    continue
                 for v in vars(part).values():
                     if isinstance(v, torch.Tensor):
                         yield v
                     elif isinstance(v, Linear):
                         yield v.weight
+                    elif isinstance(v, StackedInput):
+                        if v.linear is not None:
+                            yield v.linear.weight
+                        for _, w in v._pieces:
+                            yield w

@@ -2,13 +2,17 @@
 from .base import (FeedForward, Mixer, Norm, Part, PositionEncoding, Runtime, StepContext, part_class,
                    register_arrangement, register_feed_forward, register_mixer, register_norm, register_position)
 from .linear import Linear
-from .norm import RMSNorm
+from .norm import LayerNorm, RMSNorm
 from .position import RotaryPosition, rotary_inverse_frequencies
 from .attention import AttentionMixer
 from .swiglu import SwiGLUFeedForward
-from .block import PreNormBlock
+from .block import PreNormBlock, SandwichBlock
+from .dense import DenseFeedForward
+from .gate import SigmoidLinearGate
+from .recurrent import GatedDeltaMixer, MinGRUMixer
 
 __all__ = ["FeedForward", "Mixer", "Norm", "Part", "PositionEncoding", "Runtime", "StepContext", "part_class",
            "register_arrangement", "register_feed_forward", "register_mixer", "register_norm",
            "register_position", "Linear", "RMSNorm", "RotaryPosition", "rotary_inverse_frequencies",
-           "AttentionMixer", "SwiGLUFeedForward", "PreNormBlock"]
+           "AttentionMixer", "SwiGLUFeedForward", "PreNormBlock", "SandwichBlock", "LayerNorm", "DenseFeedForward",
+           "SigmoidLinearGate", "GatedDeltaMixer", "MinGRUMixer"]

@@ -11,7 +11,7 @@ from ..config.spec import PartSpec
 from ..csrc import ops
 from ..weights.loader import TensorDecl
 from .base import Mixer, PositionEncoding, Runtime, StepContext, register_mixer
-from .linear import Linear
+from .linear import Linear, StackedInput
 
 
 @register_mixer("attention")
@@ -26,6 +26,12 @@ class AttentionMixer(Mixer):
     every earlier key), ``scale`` (default head_dim ** -0.5, what KuiperLLama fixes,
     mha_kernel.cu:61) and ``names`` of the four projection tensors.  The three input
     projections are stacked into one matrix at load so that one product makes q, k and v.
+
+    Two options that KuiperLLama's attention does not have: ``values`` = "keys" (there is no Wv:
+    the values are the keys as projected, before their rotation) and an output gate
+    (``names['g']``: the concatenated heads are multiplied by sigmoid(Wg n) before Wo).  With
+    either, the projections live in a ``StackedInput`` (attribute ``inputs``), so that a gate on
+    the mixer's result can ride on the same product.
     """
 
     accepts_lazy_norm = True      # the q/k/v product can normalise the stream's rows itself
@@ -35,8 +41,13 @@ class AttentionMixer(Mixer):
     def manifest(cls, spec: PartSpec, prefix: str) -> Dict[str, TensorDecl]:
         hid, H, KV, hd = spec["hidden_size"], spec["num_heads"], spec["num_kv_heads"], spec["head_dim"]
         n = spec["names"]
-        return {prefix + n["q"]: TensorDecl((H * hd, hid)), prefix + n["k"]: TensorDecl((KV * hd, hid)),
-                prefix + n["v"]: TensorDecl((KV * hd, hid)), prefix + n["o"]: TensorDecl((hid, H * hd))}
+        m = {prefix + n["q"]: TensorDecl((H * hd, hid)), prefix + n["k"]: TensorDecl((KV * hd, hid)),
+             prefix + n["o"]: TensorDecl((hid, H * hd))}
+        if spec.get("values", "own") != "keys":
+            m[prefix + n["v"]] = TensorDecl((KV * hd, hid))
+        if n.get("g"):
+            m[prefix + n["g"]] = TensorDecl((H * hd, hid))
+        return m
 
     def __init__(self, spec, prefix, tensors, runtime: Runtime, position: Optional[PositionEncoding] = None):
         super().__init__(spec, prefix, tensors, runtime, position)
@@ -44,15 +55,21 @@ class AttentionMixer(Mixer):
         self.H, self.KV, self.hd = int(spec["num_heads"]), int(spec["num_kv_heads"]), int(spec["head_dim"])
         if self.H % self.KV:
             raise ValueError(f"{self.H} heads are not a multiple of {self.KV} kv heads")
-        if self.hd % 16 or self.hd > 256:
-            raise ValueError(f"head_dim {self.hd} is not supported by the attention kernels "
-                             "(multiples of 16 up to 256)")
+        if self.hd % 2 or self.hd > 256:
+            raise ValueError(f"head_dim {self.hd} is not supported by the attention kernels (even sizes up to 256)")
         self.window = spec.get("window")
         self.scale = float(spec.get("scale") or 1.0 / math.sqrt(float(self.hd)))
         n = spec["names"]
         dev, dt = runtime.device, runtime.dtype
-        stacked = torch.cat([tensors[prefix + n[k]].to(device=dev, dtype=dt) for k in ("q", "k", "v")], dim=0)
-        self.qkv = Linear(stacked, runtime)
+        self.values_are_keys = spec.get("values", "own") == "keys"
+        self.gated = bool(n.get("g"))
+        if self.values_are_keys or self.gated:
+            self.inputs = StackedInput(runtime)               # q | k | (v) | (g), then whatever rides along
+            for k in ("q", "k") + (() if self.values_are_keys else ("v",)) + (("g",) if self.gated else ()):
+                self.inputs.add(k, tensors[prefix + n[k]])
+        else:
+            stacked = torch.cat([tensors[prefix + n[k]].to(device=dev, dtype=dt) for k in ("q", "k", "v")], dim=0)
+            self.qkv = Linear(stacked, runtime)
         self.o = Linear(tensors[prefix + n["o"]], runtime)
         rot = position.rotary() if position is not None else None
         self.inv_freq, self.rotary_dim = rot if rot is not None else (None, 0)
@@ -60,7 +77,28 @@ class AttentionMixer(Mixer):
     def kv_request(self) -> Optional[KVRequest]:
         return KVRequest(kv_heads=self.KV, head_dim=self.hd, kind="full", window=self.window)
 
+    def _forward_stacked(self, x, step: StepContext, cache: CacheView) -> torch.Tensor:
+        """The form with options: rotation and cache write, attention, the output gate, Wo; q, k
+        (and v) are the leading columns of the stacked product."""
+        if hasattr(x, "dense"):
+            x = x.dense()
+        n = step.n_tokens
+        proj = self.inputs.forward(x)
+        ops.rope_kv_write(proj, self.inv_freq, self.rotary_dim, step.positions, step.token_slot, cache.block_table,
+                          cache.k if cache.writable else None, cache.v if cache.writable else None,
+                          self.H, self.KV, self.hd, values_are_keys=self.values_are_keys)
+        # rows that belong to no sequence (a small step's padding) are not written by the kernels: keep them defined
+        make = torch.empty if n == step.n_seqs else torch.zeros
+        attn = make((n, self.H * self.hd), dtype=self.runtime.dtype, device=x.device)
+        ops.attention(proj, proj.stride(0), attn, cache.k, cache.v, cache.block_table, step, self.H, self.KV, self.hd,
+                      self.scale, int(self.window or 0))
+        if self.gated:
+            ops.sigmoid_gate(attn, self.inputs.view("g"))
+        return self.o.forward(attn)
+
     def forward(self, x: torch.Tensor, step: StepContext, cache: CacheView) -> torch.Tensor:
+        if self.values_are_keys or self.gated:
+            return self._forward_stacked(x, step, cache)
         n = step.n_tokens
         qkv = self.qkv.forward(x, allow_partials=True)
         if (step.is_decode and cache.writable and n == step.n_seqs and self.inv_freq is not None

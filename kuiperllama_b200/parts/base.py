@@ -4,7 +4,7 @@ A part is built from a ``PartSpec`` (its sizes and constants), a tensor-name pre
 loaded tensors and the run's ``Runtime`` (device and compute dtype).  It never sees the
 model's configuration, so no part knows which model it is in.  A new part is a class with
 the interface below, registered under a name with ``register_mixer`` / ``register_feed_forward``
-/ ``register_norm`` / ``register_position`` / ``register_arrangement``; a ``LayerSpec`` then
+/ ``register_norm`` / ``register_position`` / ``register_gate`` / ``register_arrangement``; a ``LayerSpec`` then
 names it.
 
 ExiledOfCode/KuiperLLama's counterpart is its op layer (kuiper/include/op/layer.h:25-188):
@@ -113,6 +113,18 @@ class NormedLazy:
         return out
 
 
+@dataclass
+class PostNormed:
+    """A sublayer's result that is not in the residual stream yet and has a way to go before it is:
+    d = value * sigmoid(gate + gate_bias) where a gate is given, then d = norm(d) where a norm is
+    given, then the 32-bit sum.  The norm that reads the stream next does all of it in its own
+    kernel (``ops.norm_chain``), as it adds a plain pending delta."""
+    value: torch.Tensor                       # [n_tokens, hidden], compute dtype, any row stride
+    gate: Optional[torch.Tensor] = None       # [n_tokens, hidden] pre-activation, compute dtype, any row stride
+    gate_bias: Optional[torch.Tensor] = None  # float32 [hidden]
+    norm: Optional["Norm"] = None             # applied to the gated value; has weight, bias, eps, kind
+
+
 class Part:
     """Base of all parts."""
 
@@ -137,6 +149,8 @@ class Norm(Part):
     the stream already) and may then return ``NormedLazy`` for the part that follows."""
 
     accepts_accumulated = False
+    kind = "rmsnorm"              # what ``ops.norm_chain`` calls the norm's arithmetic
+    bias: Optional[torch.Tensor] = None
 
     def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], n_rows: int,
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -182,6 +196,21 @@ class Mixer(Part):
         raise NotImplementedError
 
 
+class ResidualGate(Part):
+    """A gate on a sublayer's result, computed from the sublayer's input h.  ``attach(part)`` is
+    called once with the sublayer it gates (it may let its projection ride on the part's input
+    product); ``pre_activation(h)`` is called after the sublayer ran on h and returns what goes
+    into ``PostNormed.gate``; ``bias`` is float32 [hidden] or None."""
+
+    bias: Optional[torch.Tensor] = None
+
+    def attach(self, part: "Part") -> None:
+        return None
+
+    def pre_activation(self, h: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+
 class FeedForward(Part):
     """``forward(x, step)``: [n_tokens, hidden] -> [n_tokens, hidden], token by token (or
     float32 partial sums [S, n_tokens, hidden], as a mixer may)."""
@@ -196,7 +225,7 @@ class FeedForward(Part):
 # ----------------------------------------------------------------------------- registries
 
 _REGISTRIES: Dict[str, Dict[str, type]] = {"mixer": {}, "feed_forward": {}, "norm": {}, "position": {},
-                                           "arrangement": {}}
+                                           "arrangement": {}, "gate": {}}
 
 
 def _register(family: str, name: str) -> Callable[[type], type]:
@@ -211,6 +240,7 @@ def register_feed_forward(name: str): return _register("feed_forward", name)
 def register_norm(name: str): return _register("norm", name)
 def register_position(name: str): return _register("position", name)
 def register_arrangement(name: str): return _register("arrangement", name)
+def register_gate(name: str): return _register("gate", name)
 
 
 def part_class(family: str, name: str) -> type:

@@ -6,7 +6,7 @@ from typing import Optional, Tuple
 import torch
 
 from ..cache import CacheView
-from .base import FeedForward, Mixer, Norm, NormedLazy, StepContext, StreamSink, register_arrangement
+from .base import FeedForward, Mixer, Norm, NormedLazy, PostNormed, ResidualGate, StepContext, StreamSink, register_arrangement
 
 
 @register_arrangement("pre_norm")
@@ -45,3 +45,49 @@ class PreNormBlock:
         out = self.feed_forward.forward(n, step)
         step.residual_sink = None
         return residual, out
+
+
+@register_arrangement("sandwich")
+class SandwichBlock:
+    """A norm before and a norm after every sublayer, and optionally a gate on its result:
+
+        h = norm1(x);  x += norm1b(gate1(h) * mixer(h))
+        h = norm2(x);  x += norm2b(gate2(h) * feed_forward(h))        (left out without a feed-forward)
+
+    with gate(h) = sigmoid(R h + r).  As in the pre-norm block the stream is float32 and no add
+    runs as a kernel of its own: a sublayer's result travels as ``PostNormed`` to the norm that
+    reads the stream next, whose kernel gates it, norms it, adds it and norms the sum.
+    KuiperLLama has the pre-norm block alone (kuiper/source/model/llama3.cpp:155-164)."""
+
+    def __init__(self, mixer_norm: Norm, mixer: Mixer, feed_forward_norm: Optional[Norm], feed_forward: Optional[FeedForward],
+                 mixer_post_norm: Optional[Norm] = None, feed_forward_post_norm: Optional[Norm] = None,
+                 mixer_gate: Optional[ResidualGate] = None, feed_forward_gate: Optional[ResidualGate] = None):
+        self.mixer_norm, self.mixer = mixer_norm, mixer
+        self.feed_forward_norm, self.feed_forward = feed_forward_norm, feed_forward
+        self.mixer_post_norm, self.feed_forward_post_norm = mixer_post_norm, feed_forward_post_norm
+        self.mixer_gate, self.feed_forward_gate = mixer_gate, feed_forward_gate
+        if mixer_gate is not None:
+            mixer_gate.attach(mixer)
+        if feed_forward_gate is not None and feed_forward is not None:
+            feed_forward_gate.attach(feed_forward)
+
+    @staticmethod
+    def _result(y, h, gate: Optional[ResidualGate], norm: Optional[Norm]) -> PostNormed:
+        if y.dim() == 3:                                 # float32 pieces of a product: their sum, once
+            y = y.sum(dim=0).to(h.dtype)
+        if gate is None:
+            return PostNormed(y, norm=norm)
+        return PostNormed(y, gate=gate.pre_activation(h), gate_bias=gate.bias, norm=norm)
+
+    def forward(self, residual: torch.Tensor, pending, step: StepContext, cache: CacheView):
+        step.residual_sink = None
+        h = self.mixer_norm.forward(residual, pending, step.n_tokens)
+        if isinstance(h, NormedLazy):
+            h = h.dense()
+        pending = self._result(self.mixer.forward(h, step, cache), h, self.mixer_gate, self.mixer_post_norm)
+        if self.feed_forward is None:
+            return residual, pending
+        h = self.feed_forward_norm.forward(residual, pending, step.n_tokens)
+        if isinstance(h, NormedLazy):
+            h = h.dense()
+        return residual, self._result(self.feed_forward.forward(h, step), h, self.feed_forward_gate, self.feed_forward_post_norm)

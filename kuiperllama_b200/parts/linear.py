@@ -53,3 +53,45 @@ class Linear:
             out = torch.empty((m, self.out_features), dtype=out_dtype or self.runtime.dtype, device=x.device)
         ops.matmul(x, self.weight, out)
         return out
+
+
+class StackedInput:
+    """Several projections of the same rows as one product: the weights are stacked along the
+    output axis once (at the first ``forward``), and every projection is a column slice of the
+    result.  A part that keeps its input projections here lets others (a residual gate that reads
+    the same rows) ``add`` theirs, which saves a product each; kernels take the slices by column
+    offset and the matrix's row stride.  (KuiperLLama runs wq, wk, wv as three products,
+    kuiper/source/model/llama3.cpp:610-639.)"""
+
+    def __init__(self, runtime: Runtime):
+        self.runtime = runtime
+        self._pieces = []                  # (name, weight) until the first forward
+        self.columns = {}                  # name -> (first column, width)
+        self.linear: Optional[Linear] = None
+        self.total = 0
+        self.last: Optional[torch.Tensor] = None     # the product of the latest forward, [m, total]
+
+    def add(self, name: str, weight: torch.Tensor) -> None:
+        if self.linear is not None:
+            raise RuntimeError("projections must be added before the first forward")
+        if name in self.columns:
+            raise ValueError(f"projection {name!r} is already stacked")
+        w = weight.to(device=self.runtime.device, dtype=self.runtime.dtype)
+        self._pieces.append((name, w))
+        self.columns[name] = (self.total, w.shape[0])
+        self.total += w.shape[0]
+
+    def column(self, name: str) -> int:
+        return self.columns[name][0]
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.linear is None:
+            self.linear = Linear(torch.cat([w for _, w in self._pieces], dim=0), self.runtime)
+            self._pieces = []
+        self.last = self.linear.forward(x)
+        return self.last
+
+    def view(self, name: str) -> torch.Tensor:
+        """The named projection of the latest forward, [m, width] with the product's row stride."""
+        c, w = self.columns[name]
+        return self.last[:, c:c + w]

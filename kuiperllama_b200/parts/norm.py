@@ -1,4 +1,4 @@
-"""RMSNorm fused with the residual add."""
+"""Norms fused with the residual add: RMSNorm and the layer norm with weight and bias."""
 from __future__ import annotations
 
 from typing import Dict, Optional
@@ -8,7 +8,7 @@ import torch
 from ..config.spec import PartSpec
 from ..csrc import ops
 from ..weights.loader import TensorDecl
-from .base import Accumulated, Norm, NormedLazy, Runtime, register_norm
+from .base import Accumulated, Norm, NormedLazy, PostNormed, Runtime, register_norm
 
 
 @register_norm("rmsnorm")
@@ -30,6 +30,8 @@ class RMSNorm(Norm):
     accepts_accumulated = True
 
     def forward(self, residual: torch.Tensor, delta, n_rows: int, rows: Optional[torch.Tensor] = None):
+        if isinstance(delta, PostNormed):
+            return chain_forward(self, residual, delta, rows)
         if isinstance(delta, Accumulated):
             # the stream holds the sum already; if the rows times this norm's weight came with it,
             # the product that follows only has to apply 1 / rms
@@ -40,3 +42,64 @@ class RMSNorm(Norm):
         out = torch.empty((n_out, self.size), dtype=self.runtime.dtype, device=residual.device)
         ops.add_rmsnorm(residual, delta, self.weight, out, self.eps, rows)
         return out
+
+
+def chain_forward(norm: Norm, residual: torch.Tensor, delta, rows: Optional[torch.Tensor]) -> torch.Tensor:
+    """``norm`` of the stream after ``delta`` (None, rows in the compute dtype, or ``PostNormed``: a
+    result that is gated and normed on its way into the stream) has been added, in one kernel."""
+    n_out = rows.numel() if rows is not None else residual.shape[0]
+    out = torch.empty((n_out, residual.shape[1]), dtype=norm.runtime.dtype, device=residual.device)
+    value = gate = gate_bias = post = None
+    if isinstance(delta, PostNormed):
+        value, gate, gate_bias = delta.value, delta.gate, delta.gate_bias
+        if delta.norm is not None:
+            post = (delta.norm.weight, delta.norm.bias, delta.norm.eps, delta.norm.kind)
+    elif delta is not None:
+        if delta.dim() == 3:                                       # float32 pieces of a product: their sum, once
+            delta = delta.sum(dim=0).to(norm.runtime.dtype)
+        value = delta
+    ops.norm_chain(residual, value, out, norm.weight, norm.bias, norm.eps, norm.kind, gate=gate, gate_bias=gate_bias,
+                   post=post, rows=rows)
+    return out
+
+
+def add_to_stream(residual: torch.Tensor, delta) -> None:
+    """Add a pending delta to the stream without a norm after it (what a caller that wants the
+    stream itself does after the last block)."""
+    if delta is None:
+        return
+    if isinstance(delta, PostNormed):
+        post = None
+        if delta.norm is not None:
+            post = (delta.norm.weight, delta.norm.bias, delta.norm.eps, delta.norm.kind)
+        ops.norm_chain(residual, delta.value, None, None, None, 0.0, "layernorm", gate=delta.gate, gate_bias=delta.gate_bias, post=post)
+    else:
+        ops.norm_chain(residual, delta, None, None, None, 0.0, "layernorm")
+
+
+@register_norm("layernorm")
+class LayerNorm(Norm):
+    """out = (x - mean) / sqrt(mean((x - mean)^2) + eps) * w + b on x = residual + delta, statistics
+    and sum in 32 bits.  Spec: ``size``, ``eps``, the weight's ``name`` and the bias's ``bias``
+    (None: no bias).  KuiperLLama has the RMS norm alone (rmsnorm_kernel.cu:70-106)."""
+
+    kind = "layernorm"
+
+    @classmethod
+    def manifest(cls, spec: PartSpec, prefix: str) -> Dict[str, TensorDecl]:
+        m = {prefix + spec["name"]: TensorDecl((spec["size"],), role="vector", init="one_plus_normal")}
+        if spec.get("bias"):
+            m[prefix + spec["bias"]] = TensorDecl((spec["size"],), role="vector")
+        return m
+
+    def __init__(self, spec, prefix, tensors, runtime: Runtime):
+        super().__init__(spec, prefix, tensors, runtime)
+        self.size = int(spec["size"])
+        self.eps = float(spec["eps"])
+        self.weight = tensors[prefix + spec["name"]].to(device=runtime.device, dtype=torch.float32).contiguous()
+        self.bias = None
+        if spec.get("bias"):
+            self.bias = tensors[prefix + spec["bias"]].to(device=runtime.device, dtype=torch.float32).contiguous()
+
+    def forward(self, residual: torch.Tensor, delta, n_rows: int, rows: Optional[torch.Tensor] = None):
+        return chain_forward(self, residual, delta, rows)
