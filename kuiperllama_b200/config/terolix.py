@@ -29,7 +29,7 @@ from .spec import LayerSpec, ModelSpec, PartSpec, default_schedule
 MIXER_TYPES = ("mingru", "attention", "delta")
 # Constants the design fixes (they are parameters of the parts, so another design may choose others).
 DELTA_UNIT_EPS = 1e-6            # inside the root when q and k are made unit vectors
-DEFAULT_MAX_POSITIONS = 1 << 20  # the design names no longest sequence; the cache's size bounds it
+DEFAULT_MAX_POSITIONS = 1 << 17  # the design names no longest sequence; "max_positions" may raise it
 
 
 def _is_int(v: Any) -> bool:

@@ -232,3 +232,21 @@ def forward_logits(w: Dict[str, torch.Tensor], c: dict, tokens: Sequence[int]) -
     x = residual_streams(w, c, tokens)[-1]
     x = layer_norm(x, w["final.norm"], w["final.norm.b"], float(c["norm"]["eps"]))
     return x @ w["embed"].T
+
+
+def attention_weights(h: torch.Tensor, w: Dict[str, torch.Tensor], prefix: str, m: dict) -> torch.Tensor:
+    """softmax weights [H, T, T] of one attention mixer on input h (what tests use to see which key a
+    query reads most)."""
+    p = prefix + "mix."
+    T = h.shape[0]
+    H, G, d = int(m["heads"]), int(m["kv_heads"]), int(m["dim"])
+    q = (h @ w[p + "q"].T).view(T, H, d)
+    k = (h @ w[p + "k"].T).view(T, G, d)
+    if m.get("rot"):
+        fr = rotary_frequencies(m["rot"])
+        q, k = rotate_half_layout(q, fr, range(T)), rotate_half_layout(k, fr, range(T))
+    out = torch.zeros(H, T, T, dtype=F)
+    for hh in range(H):
+        s = (q[:, hh, :] @ k[:, hh // (H // G), :].T) * float(m["scale"])
+        out[hh] = torch.softmax(s.masked_fill(torch.ones(T, T, dtype=torch.bool).triu(1), -math.inf), dim=-1)
+    return out
