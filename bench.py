@@ -4,6 +4,7 @@ B200, and the two other workloads of the same family (Llama-2-7B shape with ragg
 Llama-3.2-1B shape with temperature sampling).
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--batch B] [--impl reference] [--no-points]
+    python bench.py --compare terolix [--sizes 1b,8b-8-layers]      (another design beside Llama; see compare_designs)
 
 A "step" is one decode step of a batch (default 8 sequences that each hold a 512-token
 prompt, context limit 4096).  One JSON line is printed:
@@ -347,6 +348,80 @@ def run_workload(kl, cfg, name, n_seqs, lo, hi, new_tokens, temperature, pk, see
     return out
 
 
+# ---------------------------------------------------------------------------------------------- another design beside Llama
+
+def terolix_config(width, layers, heads, kv_heads, head_dim, ff, vocab):
+    """A Terolix model of ``layers`` layers in the order minGRU, minGRU, attention, delta rule, every mixer
+    as wide as the model and with the Llama shape's head counts and head size."""
+    rot = {"base": 500000.0, "dims": head_dim // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
+    kinds = {
+        "mingru": {"type": "mingru", "mixer": {"width": width}},
+        "attention": {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim,
+                                                     "scale": head_dim ** -0.5, "rot": rot}},
+        "delta": {"type": "delta", "mixer": {"heads": width // 128, "kv_heads": max(1, width // 512), "dim": 128, "vdim": 128, "conv": 4}},
+    }
+    order = ["mingru", "mingru", "attention", "delta"]
+    return {"architecture": "Terolix", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "layers": [dict(kinds[order[i % 4]], mlp={"kind": "dense", "ff": ff}) for i in range(layers)]}
+
+
+# Pairs of equal size: the Llama shape (tied classifier, a vocabulary of 32,000 so that the layers carry the
+# step) and a Terolix model of the same width, depth, heads and head size whose feed-forward is as large
+# as the Llama one's once the two gates of a layer are counted with it (2 W F + 2 W^2 = 3 W I).
+COMPARE_SIZES = {
+    "1b": dict(width=2048, layers=16, heads=32, kv_heads=8, head_dim=64, inter=8192, ff=11264),
+    "8b-8-layers": dict(width=4096, layers=8, heads=32, kv_heads=8, head_dim=128, inter=14336, ff=19456),
+}
+
+
+def compare_designs(args):
+    """``--compare terolix``: prefill (one prompt of 2,048 tokens) and decode (8 and 64 sequences after
+    512-token prompts, CUDA graphs) of Terolix beside the Llama decoder at equal size, random weights,
+    bfloat16.  Rates in tokens a second; ``hbm_frac`` is the weights' bytes over the decode step's time
+    over the copy peak, ``tc_frac`` the prefill's matrix-product flops over its time over the bf16 peak."""
+    import torch
+    import kuiperllama_b200 as kl
+    from kuiperllama_b200.config import config_from_dict
+    pk = peaks()
+    checks, out = {}, {}
+    vocab = 32000
+    clocks = ClockSampler()
+    clocks.start()
+    for name, z in COMPARE_SIZES.items():
+        if args.sizes and name not in args.sizes.split(","):
+            continue
+        llama = dict(LLAMA31_8B, hidden_size=z["width"], intermediate_size=z["inter"], num_hidden_layers=z["layers"],
+                     num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"], head_dim=z["head_dim"], vocab_size=vocab,
+                     tie_word_embeddings=True)
+        tero = terolix_config(z["width"], z["layers"], z["heads"], z["kv_heads"], z["head_dim"], z["ff"], vocab)
+        out[name] = {}
+        for design, cfg in (("llama", llama), ("terolix", tero)):
+            model = kl.random_model(config_from_dict(cfg), seed=0, dtype="bfloat16", device="cuda:0")
+            infer = kl.Inference(model, max_tokens=64 * CONTEXT, max_batch=64, max_seq_len=CONTEXT)
+            wbytes = model.weight_bytes()
+            matrix_params = wbytes / 2 - vocab * z["width"]
+            t = time_prefill(infer, warmup=3, repeats=5, seed=2, checks=checks)
+            r = {"weight_gb": round(wbytes / 1e9, 3), "prefill_tokens_per_s": round(PREFILL_LEN / t, 1), "prefill_ms": round(t * 1e3, 3),
+                 "prefill_tc_frac": round(2 * PREFILL_LEN * matrix_params / t / (pk["bf16_tflops"] * 1e12), 4)}
+            for b in (8, 64):
+                k = max(16, args.steps // 2)
+                sec, _, launches = time_decode(infer, b, k, max(args.warmup, 20), seed=3 + b, checks=checks)
+                r[f"decode_b{b}_tokens_per_s"] = round(b * k / sec, 1)
+                r[f"decode_b{b}_ms_per_step"] = round(sec / k * 1e3, 4)
+                r[f"decode_b{b}_hbm_frac"] = round(wbytes / (sec / k) / 1e9 / pk["hbm_gbs"], 4)
+                r[f"decode_b{b}_launches_per_step"] = round(launches / k, 1)
+            out[name][design] = r
+            del infer, model
+            torch.cuda.empty_cache()
+        a, b = out[name]["terolix"], out[name]["llama"]
+        out[name]["terolix_over_llama"] = {k: round(a[k] / b[k], 3) for k in a if k.endswith("tokens_per_s")}
+    print(json.dumps({"metric": "prefill and decode tok/s of Terolix beside Llama at equal size, bf16, random weights",
+                      "impl": "ours", "n_gpus": 1, "dtype": "bf16", "data": "synthetic: random weights N(0, 0.02), uniform random token ids",
+                      "prompt_len": PROMPT_LEN, "prefill_len": PREFILL_LEN, "peaks": pk["source"], "sizes": out,
+                      "clocks": clocks.stop(), "checks": checks}))
+    return 0
+
+
 def reference_arm(args):
     """ExiledOfCode/KuiperLLama is a CMake C++ project without a Python package definition, and
     its build fetches glog, armadillo, sentencepiece and gtest over the network; it cannot be
@@ -372,9 +447,14 @@ def main():
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--no-points", action="store_true",
                     help="only the headline: skip the prefill, the batch 1, 64 and 128 points and the two other workloads")
+    ap.add_argument("--compare", default=None, choices=["terolix"],
+                    help="instead of the default workload: this design beside Llama at equal size (prefill and decode rates)")
+    ap.add_argument("--sizes", default="", help="with --compare: which of the sizes to run, with commas (default: all)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.compare:
+        return compare_designs(args)
     if args.gpus != 1:
         print(f"bench.py measures one GPU: this library has no multi-GPU path (--gpus {args.gpus} refused)")
         return 2

@@ -255,6 +255,10 @@ def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor) -> None:
 
 # --------------------------------------------------------------------------- recurrent mixers
 
+MINGRU_CHUNK = 64              # equals MG_CHUNK in recurrent.cu
+MINGRU_CHUNKED_FROM = 256      # tokens of the longest sequence from which a step takes the chunked scan
+
+
 def mingru_scan(proj: torch.Tensor, z_col: int, x_col: int, g_col: int, bias_z: Optional[torch.Tensor], bias_x: Optional[torch.Tensor],
                 state: torch.Tensor, out: torch.Tensor, step, width: int) -> None:
     """The minGRU recurrence over a ragged step.  ``proj`` [rows, >= 3 width] holds the z, x and gate
@@ -265,9 +269,17 @@ def mingru_scan(proj: torch.Tensor, z_col: int, x_col: int, g_col: int, bias_z: 
     _need(out.is_contiguous() and out.dtype == proj.dtype and out.shape[1] == width and out.shape[0] >= step.n_tokens, "mingru_scan: out")
     for b in (bias_z, bias_x):
         _need(b is None or (b.dtype == torch.float32 and b.numel() == width and b.is_contiguous()), "mingru_scan: bias")
+    # Steps with long sequences run in chunks of 64 tokens (three passes, every chunk at once); a thread that
+    # walks its channel alone is faster while a sequence brings few chunks.
+    scratch, launches = None, 1
+    if step.max_new >= MINGRU_CHUNKED_FROM:
+        chunks = -(-step.max_new // MINGRU_CHUNK)
+        scratch = torch.empty(step.n_seqs * chunks * 3 * width, dtype=torch.float32, device=proj.device)
+        launches = 3
     _check(lib("recurrent").kl_mingru_scan(_ptr(proj), ctypes.c_longlong(proj.stride(0)), z_col, x_col, g_col, _ptr(bias_z), _ptr(bias_x),
                                            _ptr(state), ctypes.c_longlong(state.stride(0)), _ptr(out), _ptr(step.cu_tokens),
-                                           _ptr(step.seq_slots), step.n_seqs, width, dtype_code(proj.dtype), _stream()), "mingru_scan")
+                                           _ptr(step.seq_slots), step.n_seqs, step.max_new, _ptr(scratch), width,
+                                           dtype_code(proj.dtype), _stream()), "mingru_scan", launches)
 
 
 def gated_delta_rule(proj: torch.Tensor, conv_col: int, b_col: int, a_col: int, conv_weight: torch.Tensor, A_log: torch.Tensor,

@@ -64,6 +64,78 @@ mingru_scan_kernel(const T* __restrict__ proj, long long ld, int z_col, int x_co
     *st = S;
 }
 
+// The same recurrence for steps with long sequences, in three passes over chunks of MG_CHUNK tokens
+// (s_t = a_t s_(t-1) + b_t with a = 1 - z, b = z c composes: a chunk maps its incoming state s to
+// A s + B).  Pass 1, a thread per (chunk, channel): A and B of the chunk.  Pass 2, a thread per
+// (sequence, channel): the state at the start of every chunk, chunk after chunk, and the slot's state
+// after the step.  Pass 3, a thread per (chunk, channel): the chunk again from its true start, writing
+// out.  Chunks are counted per sequence from the step's first token; chunk c of sequence s is entry
+// chunk_first[s] + c of the (A, B) arrays, which the host sizes for the step.
+constexpr int MG_CHUNK = 64;
+
+template <typename T>
+__device__ __forceinline__ void mingru_gates(const T* __restrict__ row, int z_col, int x_col, int c, float biasz, float biasx,
+                                             float& a, float& b) {
+    const float z = sigmoidf_(to_f32(row[z_col + c]) + biasz);
+    const float u = to_f32(row[x_col + c]) + biasx;
+    a = 1.0f - z;
+    b = z * (u >= 0.f ? u + 0.5f : sigmoidf_(u));
+}
+
+template <typename T, int PASS>
+__global__ void __launch_bounds__(128)
+mingru_chunk_kernel(const T* __restrict__ proj, long long ld, int z_col, int x_col, int g_col, const float* __restrict__ bz,
+                    const float* __restrict__ bx, float* __restrict__ state, long long state_ld, T* __restrict__ out,
+                    float* __restrict__ AB, const int* __restrict__ cu_tokens, const int* __restrict__ seq_slots, int width,
+                    int max_chunks) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= width) return;
+    const int s = blockIdx.z;
+    const int r0 = cu_tokens[s], r1 = cu_tokens[s + 1];
+    const int n_chunks = (r1 - r0 + MG_CHUNK - 1) / MG_CHUNK;
+    const float biasz = bz ? bz[c] : 0.f, biasx = bx ? bx[c] : 0.f;
+    // (A, B, start state) of chunk k of sequence s: three floats per channel at entry s * max_chunks + k
+    float* ab = AB + ((size_t)s * max_chunks) * 3 * width + c;
+    if (PASS == 2) {
+        float* st = state + (size_t)seq_slots[s] * state_ld + c;
+        float S = *st;
+        for (int k = 0; k < n_chunks; ++k) {
+            float* e = ab + (size_t)k * 3 * width;
+            e[2 * width] = S;
+            S = fmaf(e[0], S, e[width]);
+        }
+        if (n_chunks > 0) *st = S;
+        return;
+    }
+    const int k = blockIdx.y;
+    if (k >= n_chunks) return;
+    float* e = ab + (size_t)k * 3 * width;
+    const int t0 = r0 + k * MG_CHUNK, t1 = min(t0 + MG_CHUNK, r1);
+    if (PASS == 1) {
+        float A = 1.f, B = 0.f;
+        for (int r = t0; r < t1; ++r) {
+            float a, b;
+            mingru_gates(proj + (size_t)r * ld, z_col, x_col, c, biasz, biasx, a, b);
+            A *= a;
+            B = fmaf(a, B, b);
+        }
+        e[0] = A;
+        e[width] = B;
+    } else {
+        float S = e[2 * width];
+        for (int r = t0; r < t1; ++r) {
+            const T* row = proj + (size_t)r * ld;
+            float a, b;
+            mingru_gates(row, z_col, x_col, c, biasz, biasx, a, b);
+            S = fmaf(a, S, b);
+            const float g = to_f32(row[g_col + c]);
+            out[(size_t)r * width + c] = from_f32<T>(S * (g * sigmoidf_(g)));
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------------ gated delta rule
 // Step 1, one CTA per token: the short convolution and SiLU over the C = 2 G d + H dv channels of
 // q | k | v, unit length for each q and k head (q also times q_scale), and the token's beta and
@@ -118,6 +190,10 @@ delta_prepare_kernel(const T* __restrict__ proj, long long ld, int conv_col, int
 // another column, so a CTA owns some columns of one head of one sequence and walks the tokens in
 // order.  A column is cut over LPC adjacent lanes of 32 key elements each (d <= 32 LPC), kept in
 // registers; the tokens' k, q, v, beta and decay come through shared memory a tile of tokens at a time.
+// The read-out after the write, o = S_new^T q, is taken from the state before it:
+//     S_new^T q = g S^T q + (k . q) u,
+// so that both products with the old state (S^T k and S^T q) run side by side and only one
+// multiply-add per element lies between one token's products and the next one's.
 // Before it starts, the first CTA of a sequence moves the convolution state on (the raw projections
 // of the step's last taps - 1 tokens; step 1 has finished with the old one).
 constexpr int DR_THREADS = 128, DR_TILE = 8, DR_DPT = 32;
@@ -133,7 +209,7 @@ delta_rule_kernel(const float* __restrict__ prep, const float* __restrict__ bg, 
     constexpr int COLS = DR_THREADS / LPC;
     constexpr int DP = DR_DPT * LPC;                      // padded key size
     constexpr int DPS = (DR_DPT + 1) * LPC;               // in shared memory every part starts one bank further on
-    __shared__ float ks[DR_TILE][DPS], qs[DR_TILE][DPS], vs[DR_TILE][COLS], bs[DR_TILE], gs[DR_TILE];
+    __shared__ float ks[DR_TILE][DPS], qs[DR_TILE][DPS], vs[DR_TILE][COLS], bs[DR_TILE], gs[DR_TILE], kqs[DR_TILE];
     const int s = blockIdx.z, h = blockIdx.y;
     const int r0 = cu_tokens[s], r1 = cu_tokens[s + 1];
     if (r1 <= r0) return;
@@ -177,26 +253,37 @@ delta_rule_kernel(const float* __restrict__ prep, const float* __restrict__ bg, 
             bs[threadIdx.x] = bg[(size_t)(t0 + threadIdx.x) * 2 * H + h];
             gs[threadIdx.x] = bg[(size_t)(t0 + threadIdx.x) * 2 * H + H + h];
         }
+        {                                                  // k . q of every token of the tile, a warp each
+            const int lane = threadIdx.x & 31;
+            for (int tt = threadIdx.x >> 5; tt < nt; tt += DR_THREADS / 32) {
+                const float* p = prep + (size_t)(t0 + tt) * C;
+                float a = 0.f;
+                for (int i = lane; i < d; i += 32) a = fmaf(p[(size_t)(G + g) * d + i], p[(size_t)g * d + i], a);
+                a = warp_sum(a);
+                if (lane == 0) kqs[tt] = a;
+            }
+        }
         __syncthreads();
         for (int tt = 0; tt < nt; ++tt) {
             const float* kk = &ks[tt][part * (DR_DPT + 1)];
             const float* qq = &qs[tt][part * (DR_DPT + 1)];
             const float decay = gs[tt], beta = bs[tt];
-            float sk = 0.f;
-#pragma unroll
-            for (int i = 0; i < DR_DPT; ++i) sk = fmaf(S[i], kk[i], sk);
-#pragma unroll
-            for (int o = LPC >> 1; o > 0; o >>= 1) sk += __shfl_xor_sync(0xffffffffu, sk, o);
-            const float u = beta * (vs[tt][col_local] - decay * sk);
-            float oq = 0.f;
+            float sk[4] = {0.f, 0.f, 0.f, 0.f}, sq[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int i = 0; i < DR_DPT; ++i) {
-                S[i] = fmaf(kk[i], u, decay * S[i]);
-                oq = fmaf(S[i], qq[i], oq);
+                sk[i & 3] = fmaf(S[i], kk[i], sk[i & 3]);
+                sq[i & 3] = fmaf(S[i], qq[i], sq[i & 3]);
             }
+            float skt = (sk[0] + sk[1]) + (sk[2] + sk[3]), sqt = (sq[0] + sq[1]) + (sq[2] + sq[3]);
 #pragma unroll
-            for (int o = LPC >> 1; o > 0; o >>= 1) oq += __shfl_xor_sync(0xffffffffu, oq, o);
-            if (live && part == 0) out[((size_t)(t0 + tt) * H + h) * dv + col] = oq;
+            for (int o = LPC >> 1; o > 0; o >>= 1) {
+                skt += __shfl_xor_sync(0xffffffffu, skt, o);
+                sqt += __shfl_xor_sync(0xffffffffu, sqt, o);
+            }
+            const float u = beta * (vs[tt][col_local] - decay * skt);
+#pragma unroll
+            for (int i = 0; i < DR_DPT; ++i) S[i] = fmaf(kk[i], u, decay * S[i]);
+            if (live && part == 0) out[((size_t)(t0 + tt) * H + h) * dv + col] = fmaf(kqs[tt], u, decay * sqt);
         }
     }
     if (live) {
@@ -211,11 +298,29 @@ delta_rule_kernel(const float* __restrict__ prep, const float* __restrict__ bg, 
 using namespace kl;
 
 // proj: compute dtype [rows, ld]; z, x, g at columns z_col, x_col, g_col (width each); out [rows, width].
+// max_new: no sequence brings more rows.  With `chunk_scratch` (float32 [n_seqs * ceil(max_new / 64) * 3 * width]) and a step
+// long enough to gain from it, the three-pass chunked form runs (3 launches), else one thread walks each channel.
+KL_API int kl_mingru_chunk_tokens() { return MG_CHUNK; }
+
 KL_API int kl_mingru_scan(const void* proj, long long ld, int z_col, int x_col, int g_col, const float* bz, const float* bx,
                           float* state, long long state_ld, void* out, const int* cu_tokens, const int* seq_slots, int n_seqs,
-                          int width, int dtype, cudaStream_t stream) {
+                          int max_new, float* chunk_scratch, int width, int dtype, cudaStream_t stream) {
     if (n_seqs <= 0 || width <= 0) return KL_OK;
     if (n_seqs > 65535) return KL_ERR_BAD_SIZE;
+    if (chunk_scratch != nullptr) {
+        const int max_chunks = (max_new + MG_CHUNK - 1) / MG_CHUNK;
+        if (max_chunks > 65535) return KL_ERR_BAD_SIZE;
+        const dim3 g13((width + 127) / 128, max_chunks, n_seqs), g2((width + 127) / 128, 1, n_seqs);
+#define KL_MG(T, PASS, GRID)                                                                                                      \
+        launch_kernel(mingru_chunk_kernel<T, PASS>, GRID, 128, 0, stream, (const T*)proj, ld, z_col, x_col, g_col, bz, bx, state, state_ld, \
+                      (T*)out, chunk_scratch, cu_tokens, seq_slots, width, max_chunks)
+        if (dtype == KL_F32) { KL_MG(float, 1, g13); KL_MG(float, 2, g2); KL_MG(float, 3, g13); }
+        else if (dtype == KL_BF16) { KL_MG(bf16, 1, g13); KL_MG(bf16, 2, g2); KL_MG(bf16, 3, g13); }
+        else return KL_ERR_BAD_DTYPE;
+#undef KL_MG
+        KL_LAUNCH_CHECK();
+        return KL_OK;
+    }
     const dim3 grid((width + 127) / 128, n_seqs);
     if (dtype == KL_F32)
         launch_kernel(mingru_scan_kernel<float>, grid, 128, 0, stream, (const float*)proj, ld, z_col, x_col, g_col, bz, bx, state, state_ld,

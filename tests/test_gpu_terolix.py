@@ -233,6 +233,29 @@ def test_long_decoding(models, dtype):
     assert_logits(got, oracle_logits(folder, toks), dtype, "long decoding")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["mixed", "wide"])
+def test_long_prompts_in_one_step(models, name, dtype):
+    """Prompts of 300, 257, 256 and 70 tokens in one step (from 256 tokens on the minGRU runs chunk by
+    chunk in three passes; the last chunks are part full, one sequence has a single whole chunk more
+    than the threshold), then a portion of 259 more for the first, then a token each."""
+    model, folder = models(name, dtype, seed=1)
+    V = CONFIGS[name]["vocab"]
+    seqs = [tokens(n, V, seed=75 + i) for i, n in enumerate((300 + 259 + 1, 257 + 1, 256 + 1, 70 + 1))]
+    lens = [300, 257, 256, 70]
+    refs = [oracle_logits(folder, s) for s in seqs]
+    engine = _engine(model, max_tokens=64 * 24)
+    with torch.inference_mode():
+        slots = [engine.alloc_slot() for _ in seqs]
+        got = engine.step([_inputs(sl, s[:n]) for sl, s, n in zip(slots, seqs, lens)])
+        assert_logits(got, torch.cat([r[:n] for r, n in zip(refs, lens)]), dtype, f"{name}: long prompts")
+        got = engine.step([_inputs(slots[0], seqs[0][300:559])])
+        assert_logits(got, refs[0][300:559], dtype, f"{name}: a long portion")
+        got = engine.step([_inputs(sl, [s[-1]]) for sl, s in zip(slots, seqs)])
+        assert_logits(got, torch.stack([r[-1] for r in refs]), dtype, f"{name}: the tokens after")
+    engine.check_device_errors()
+
+
 # ----------------------------------------------------------------------------- a far key that matters
 
 def _needle_model(folders, models, dtype):
