@@ -194,16 +194,20 @@ def check_after(infer, logits, what, checks):
 def verify_graph_replay(eng, slots, tokens):
     """One decode step twice from the same state: launched kernel by kernel (the first step of a
     batch size, which also captures the graph), then replayed from the graph after the lengths
-    were set back.  Both write the same keys and values to the same places.  Returns the largest
+    were set back (and per-slot state, where a model has some, put back).  Both write the same keys and values to the same places.  Returns the largest
     difference between the two steps' logits (0 expected: the same kernels on the same data)."""
     import torch
     n = len(slots)
     assert n not in eng.graph_sizes(), "the graph of this batch size exists already"
     before = [eng.cache.lengths[s] for s in slots]
+    index = torch.tensor(slots, dtype=torch.int64, device=eng.device)
+    states = {i: st.index_select(0, index) for i, st in eng.cache.states.items()}     # recurrent mixers: the step moves their state on
     eager = eng.decode_step(slots, tokens).clone()
     assert n in eng.graph_sizes()
     for s, b in zip(slots, before):
         eng.cache.lengths[s] = b
+    for i, saved in states.items():
+        eng.cache.states[i].index_copy_(0, index, saved)
     replayed = eng.decode_step(slots, tokens)
     if not torch.equal(eager.argmax(dim=1), replayed.argmax(dim=1)):
         raise BenchCheckError(f"batch {n}: the step replayed from its CUDA graph chose other tokens than the same step without a graph")

@@ -30,6 +30,27 @@ __global__ void activation_kernel(const T* __restrict__ x, long long ld_x, T* __
     }
 }
 
+// The same, 16 bytes per access (rows whose starts and widths are multiples of 16 bytes).
+template <typename T>
+__global__ void activation_vec_kernel(const T* __restrict__ x, long long ld_x, T* __restrict__ out, long long ld_out, int tokens, int n,
+                                      int kind, const float* __restrict__ params) {
+    pdl_launch_dependents();
+    pdl_wait();
+    constexpr int V = 16 / sizeof(T);
+    const float a_pos = params ? params[0] : 0.f, a_neg = params ? params[1] : 0.f;
+    const int nv = n / V;
+    const size_t total = (size_t)tokens * nv;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / nv;
+        const int i = (int)(idx - t * nv) * V;
+        uint4 raw = *reinterpret_cast<const uint4*>(x + t * ld_x + i);
+        T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+        for (int k = 0; k < V; ++k) e[k] = from_f32<T>(activate(to_f32(e[k]), kind, a_pos, a_neg));
+        *reinterpret_cast<uint4*>(out + t * ld_out + i) = raw;
+    }
+}
+
 // x[t, i] *= sigmoid(gate[t, i]) in place.
 template <typename T>
 __global__ void sigmoid_gate_kernel(T* __restrict__ x, long long ld_x, const T* __restrict__ gate, long long ld_gate, int tokens, int n) {
@@ -53,13 +74,22 @@ KL_API int kl_activation(const void* x, long long ld_x, void* out, long long ld_
     if (tokens <= 0 || n <= 0) return KL_OK;
     if (kind < ACT_XIELU || kind > ACT_SILU || (kind == ACT_XIELU && params == nullptr)) return KL_ERR_BAD_SIZE;
     const int threads = 256;
+    if (dtype != KL_F32 && dtype != KL_BF16) return KL_ERR_BAD_DTYPE;
+    const int v = dtype == KL_F32 ? 4 : 8;
+    if (n % v == 0 && ld_x % v == 0 && ld_out % v == 0 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0) {
+        const int blocks = kl::strided_grid((size_t)tokens * (n / v), threads, 16);
+        if (dtype == KL_F32)
+            launch_kernel(activation_vec_kernel<float>, blocks, threads, 0, stream, (const float*)x, ld_x, (float*)out, ld_out, tokens, n, kind, params);
+        else
+            launch_kernel(activation_vec_kernel<bf16>, blocks, threads, 0, stream, (const bf16*)x, ld_x, (bf16*)out, ld_out, tokens, n, kind, params);
+        KL_LAUNCH_CHECK();
+        return KL_OK;
+    }
     const int blocks = kl::strided_grid((size_t)tokens * n, threads, 16);
     if (dtype == KL_F32)
         launch_kernel(activation_kernel<float>, blocks, threads, 0, stream, (const float*)x, ld_x, (float*)out, ld_out, tokens, n, kind, params);
-    else if (dtype == KL_BF16)
-        launch_kernel(activation_kernel<bf16>, blocks, threads, 0, stream, (const bf16*)x, ld_x, (bf16*)out, ld_out, tokens, n, kind, params);
     else
-        return KL_ERR_BAD_DTYPE;
+        launch_kernel(activation_kernel<bf16>, blocks, threads, 0, stream, (const bf16*)x, ld_x, (bf16*)out, ld_out, tokens, n, kind, params);
     KL_LAUNCH_CHECK();
     return KL_OK;
 }

@@ -43,9 +43,135 @@ __device__ __forceinline__ void norm_in_place(float* buf, int n, const float* __
     }
 }
 
+// Four neighbouring elements of a row in the compute dtype, as floats.
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+    static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Vec4<bf16> {
+    static __device__ __forceinline__ float4 load(const bf16* p) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+    static __device__ __forceinline__ void store(bf16* p, float4 v) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 raw;
+        raw.x = *reinterpret_cast<uint32_t*>(&a);
+        raw.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = raw;
+    }
+};
+
+// One norm over a row that lies in registers, VPT float4 per thread (lanes beyond the row hold zeros and
+// stay out of the sums).
+template <int THREADS, int VPT>
+__device__ __forceinline__ void norm_in_registers(float4 (&v)[VPT], int n4, int n, const float* __restrict__ w,
+                                                  const float* __restrict__ b, float eps, int kind, float* scratch) {
+    float mean = 0.f;
+    if (kind == NORM_LAYER) {
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) s += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+        mean = block_sum(s, scratch) / (float)n;
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        if ((int)threadIdx.x + j * THREADS < n4) {
+            const float a = v[j].x - mean, c = v[j].y - mean, e = v[j].z - mean, f = v[j].w - mean;
+            ss += (a * a + c * c) + (e * e + f * f);
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int i4 = threadIdx.x + j * THREADS;
+        if (i4 < n4) {
+            const float4 ww = *reinterpret_cast<const float4*>(w + 4 * i4);
+            float4 y = make_float4((v[j].x - mean) * inv * ww.x, (v[j].y - mean) * inv * ww.y, (v[j].z - mean) * inv * ww.z,
+                                   (v[j].w - mean) * inv * ww.w);
+            if (b != nullptr) {
+                const float4 bb = *reinterpret_cast<const float4*>(b + 4 * i4);
+                y.x += bb.x; y.y += bb.y; y.z += bb.z; y.w += bb.w;
+            }
+            v[j] = y;
+        }
+    }
+}
+
+// The chain with the row in registers and 8- or 16-byte accesses: rows of hidden % 4 == 0 elements up to
+// 4 THREADS VPT whose pointers and strides are aligned for it.  `partials`: the delta as float32 pieces
+// [n_partials][rows][hidden] of a product whose K range was cut, added in ascending order.
+template <typename T, int THREADS, int VPT>
+__global__ void __launch_bounds__(THREADS)
+norm_chain_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta, long long delta_ld,
+                      const float* __restrict__ partials, int n_partials, long long partial_stride,
+                      const T* __restrict__ gate, long long gate_ld, const float* __restrict__ gate_bias,
+                      const float* __restrict__ post_w, const float* __restrict__ post_b, float post_eps, int post_kind,
+                      const float* __restrict__ w, const float* __restrict__ b, float eps, int kind,
+                      T* __restrict__ out, const int* __restrict__ rows, int hidden) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const int s = rows ? rows[r] : r;
+    const int n4 = hidden >> 2;
+    float* x = residual + (size_t)s * hidden;
+    const bool adds = delta != nullptr || n_partials > 0;
+    float4 v[VPT], xr[VPT];
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int i4 = threadIdx.x + j * THREADS;
+        v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        xr[j] = v[j];
+        if (i4 < n4) {
+            xr[j] = *reinterpret_cast<const float4*>(x + 4 * i4);
+            if (delta != nullptr) v[j] = Vec4<T>::load(delta + (size_t)s * delta_ld + 4 * i4);
+            for (int z = 0; z < n_partials; ++z) {
+                const float4 p = *reinterpret_cast<const float4*>(partials + (size_t)z * partial_stride + (size_t)s * hidden + 4 * i4);
+                v[j].x += p.x; v[j].y += p.y; v[j].z += p.z; v[j].w += p.w;
+            }
+            if (gate != nullptr) {
+                float4 a = Vec4<T>::load(gate + (size_t)s * gate_ld + 4 * i4);
+                if (gate_bias != nullptr) {
+                    const float4 gb = *reinterpret_cast<const float4*>(gate_bias + 4 * i4);
+                    a.x += gb.x; a.y += gb.y; a.z += gb.z; a.w += gb.w;
+                }
+                v[j].x *= 1.0f / (1.0f + expf(-a.x)); v[j].y *= 1.0f / (1.0f + expf(-a.y));
+                v[j].z *= 1.0f / (1.0f + expf(-a.z)); v[j].w *= 1.0f / (1.0f + expf(-a.w));
+            }
+        }
+    }
+    if (adds) {
+        if (post_w != nullptr) norm_in_registers<THREADS, VPT>(v, n4, hidden, post_w, post_b, post_eps, post_kind, scratch);
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int i4 = threadIdx.x + j * THREADS;
+            v[j].x += xr[j].x; v[j].y += xr[j].y; v[j].z += xr[j].z; v[j].w += xr[j].w;
+            if (i4 < n4 && rows == nullptr) *reinterpret_cast<float4*>(x + 4 * i4) = v[j];
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) v[j] = xr[j];
+    }
+    if (out == nullptr) return;
+    norm_in_registers<THREADS, VPT>(v, n4, hidden, w, b, eps, kind, scratch);
+    T* o = out + (size_t)r * hidden;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int i4 = threadIdx.x + j * THREADS;
+        if (i4 < n4) Vec4<T>::store(o + 4 * i4, v[j]);
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 norm_chain_kernel(float* __restrict__ residual, const T* __restrict__ delta, long long delta_ld,
+                  const float* __restrict__ partials, int n_partials, long long partial_stride,
                   const T* __restrict__ gate, long long gate_ld, const float* __restrict__ gate_bias,
                   const float* __restrict__ post_w, const float* __restrict__ post_b, float post_eps, int post_kind,
                   const float* __restrict__ w, const float* __restrict__ b, float eps, int kind,
@@ -58,11 +184,12 @@ norm_chain_kernel(float* __restrict__ residual, const T* __restrict__ delta, lon
     const int r = blockIdx.x;
     const int s = rows ? rows[r] : r;
     float* x = residual + (size_t)s * hidden;
-    if (delta != nullptr) {
-        const T* d = delta + (size_t)s * delta_ld;
+    if (delta != nullptr || n_partials > 0) {
+        const T* d = delta ? delta + (size_t)s * delta_ld : nullptr;
         const T* g = gate ? gate + (size_t)s * gate_ld : nullptr;
         for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-            float v = to_f32(d[i]);
+            float v = d ? to_f32(d[i]) : 0.f;
+            for (int z = 0; z < n_partials; ++z) v += partials[(size_t)z * partial_stride + (size_t)s * hidden + i];
             if (g != nullptr) {
                 const float a = to_f32(g[i]) + (gate_bias ? gate_bias[i] : 0.f);
                 v *= 1.0f / (1.0f + expf(-a));
@@ -122,12 +249,40 @@ using namespace kl;
 
 // delta, gate, out: compute dtype (`dtype`); everything else float32.  Null pointers switch steps off:
 // no delta (nothing is added), no gate, no post norm (post_w null), no output (out null: only the sum).
-KL_API int kl_norm_chain(float* residual, const void* delta, long long delta_ld, const void* gate, long long gate_ld,
+KL_API int kl_norm_chain(float* residual, const void* delta, long long delta_ld, const float* partials, int n_partials,
+                         long long partial_stride, const void* gate, long long gate_ld,
                          const float* gate_bias, const float* post_w, const float* post_b, float post_eps, int post_kind,
                          const float* w, const float* b, float eps, int kind, void* out, const int* rows, int n_rows,
                          int hidden, int dtype, cudaStream_t stream) {
     if (n_rows <= 0) return KL_OK;
     if (hidden <= 0 || (out != nullptr && w == nullptr)) return KL_ERR_BAD_SIZE;
+    if (n_partials < 0 || (n_partials > 0 && (partials == nullptr || delta != nullptr))) return KL_ERR_BAD_SIZE;
+    const bool bf = dtype == KL_BF16;
+    if (dtype != KL_F32 && !bf) return KL_ERR_BAD_DTYPE;
+    {
+        // the form with the row in registers, where everything is aligned for 8-byte (bfloat16) or 16-byte (float) accesses
+        const uintptr_t m = bf ? 7 : 15;
+        auto ok_t = [&](const void* p, long long ld) { return p == nullptr || ((((uintptr_t)p) & m) == 0 && ld % 4 == 0); };
+        auto ok_f = [&](const void* p) { return (((uintptr_t)p) & 15) == 0; };
+        const int n4 = hidden / 4;
+        if (hidden % 4 == 0 && n4 <= 256 * 8 && ok_t(delta, delta_ld) && ok_t(gate, gate_ld) && ok_t(out, hidden) && ok_f(residual) &&
+            ok_f(partials) && ok_f(gate_bias) && ok_f(post_w) && ok_f(post_b) && ok_f(w) && ok_f(b)) {
+#define KL_VEC(T, THREADS, VPT)                                                                                              \
+            launch_kernel(norm_chain_vec_kernel<T, THREADS, VPT>, n_rows, THREADS, 0, stream, residual, (const T*)delta, delta_ld, partials, \
+                          n_partials, partial_stride, (const T*)gate, gate_ld, gate_bias, post_w, post_b, post_eps, post_kind, w, b, eps, kind, \
+                          (T*)out, rows, hidden)
+#define KL_VEC_BY_SIZE(T)                                                                                                    \
+            do {                                                                                                             \
+                if (n4 <= 64) KL_VEC(T, 64, 1); else if (n4 <= 128) KL_VEC(T, 128, 1); else if (n4 <= 256) KL_VEC(T, 256, 1);        \
+                else if (n4 <= 512) KL_VEC(T, 256, 2); else if (n4 <= 1024) KL_VEC(T, 256, 4); else KL_VEC(T, 256, 8);             \
+            } while (0)
+            if (bf) KL_VEC_BY_SIZE(bf16); else KL_VEC_BY_SIZE(float);
+#undef KL_VEC_BY_SIZE
+#undef KL_VEC
+            KL_LAUNCH_CHECK();
+            return KL_OK;
+        }
+    }
     if ((kind != NORM_LAYER && kind != NORM_RMS) || (post_kind != NORM_LAYER && post_kind != NORM_RMS)) return KL_ERR_BAD_SIZE;
     const size_t smem = (size_t)(hidden + 33) * sizeof(float);
     if (smem > 200 * 1024) return KL_ERR_BAD_SIZE;
@@ -135,7 +290,7 @@ KL_API int kl_norm_chain(float* residual, const void* delta, long long delta_ld,
 #define KL_CHAIN(T)                                                                                                        \
     do {                                                                                                                   \
         if (smem > 48 * 1024) KL_CUDA(cudaFuncSetAttribute(norm_chain_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        launch_kernel(norm_chain_kernel<T>, n_rows, threads, smem, stream, residual, (const T*)delta, delta_ld, (const T*)gate, gate_ld, \
+        launch_kernel(norm_chain_kernel<T>, n_rows, threads, smem, stream, residual, (const T*)delta, delta_ld, partials, n_partials, partial_stride, (const T*)gate, gate_ld, \
                       gate_bias, post_w, post_b, post_eps, post_kind, w, b, eps, kind, (T*)out, rows, hidden);                \
     } while (0)
     if (dtype == KL_F32) KL_CHAIN(float);

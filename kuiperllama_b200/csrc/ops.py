@@ -189,19 +189,25 @@ def norm_chain(residual: torch.Tensor, delta: Optional[torch.Tensor], out: Optio
     """d = delta * sigmoid(gate + gate_bias); d = post-norm(d); x = residual + d (written back unless
     ``rows``); out = norm(x).  Every step but the last is optional: ``delta`` None adds nothing,
     ``post`` = (weight, bias or None, eps, kind) or None, ``out`` None only updates the stream.
-    ``delta`` and ``gate`` are [n, hidden] in the compute dtype with any row stride."""
+    ``delta`` and ``gate`` are [n, hidden] in the compute dtype with any row stride; ``delta`` may also be
+    float32 pieces [S, n, hidden] of a product whose K range was cut (their sum is the delta)."""
     _cuda(residual, delta, out, weight, bias, gate, gate_bias, rows)
     _i32(rows, "rows")
     hidden = residual.shape[-1]
     n = rows.numel() if rows is not None else residual.shape[0]
     _need(residual.dtype == torch.float32 and residual.is_contiguous(), "norm_chain: the residual stream is float32")
+    parts, n_parts, stride = None, 0, 0
+    if _partials(delta):
+        _need(delta.dtype == torch.float32 and delta.is_contiguous() and tuple(delta.shape[1:]) == tuple(residual.shape),
+              "norm_chain: pieces must be float32 [S, rows, hidden]")
+        parts, n_parts, stride, delta = delta, delta.shape[0], delta.shape[1] * delta.shape[2], None
     if dtype is None:
-        dtype = out.dtype if out is not None else delta.dtype
+        dtype = next((t.dtype for t in (out, delta, gate) if t is not None), torch.float32)
     for t, nm in ((delta, "delta"), (gate, "gate")):
         if t is not None:
             _need(t.dtype == dtype and t.dim() == 2 and t.shape[1] == hidden and t.stride(1) == 1 and t.shape[0] >= residual.shape[0],
                   f"norm_chain: {nm} must be [rows, hidden] in the compute dtype")
-    _need(gate is None or delta is not None, "norm_chain: a gate needs something to gate")
+    _need(gate is None or delta is not None or parts is not None, "norm_chain: a gate needs something to gate")
     for t in (weight, bias, gate_bias) + (tuple(post[:2]) if post is not None else ()):
         _need(t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == hidden), "norm_chain: float32 [hidden] vectors")
     if out is not None:
@@ -209,7 +215,8 @@ def norm_chain(residual: torch.Tensor, delta: Optional[torch.Tensor], out: Optio
               "norm_chain: output shape")
     pw, pb, peps, pkind = post if post is not None else (None, None, 0.0, kind)
     _check(lib("norms").kl_norm_chain(
-        _ptr(residual), _ptr(delta), ctypes.c_longlong(delta.stride(0) if delta is not None else 0), _ptr(gate),
+        _ptr(residual), _ptr(delta), ctypes.c_longlong(delta.stride(0) if delta is not None else 0), _ptr(parts), n_parts,
+        ctypes.c_longlong(stride), _ptr(gate),
         ctypes.c_longlong(gate.stride(0) if gate is not None else 0), _ptr(gate_bias), _ptr(pw), _ptr(pb), ctypes.c_float(peps),
         NORM_KINDS[pkind], _ptr(weight), _ptr(bias), ctypes.c_float(eps), NORM_KINDS[kind], _ptr(out), _ptr(rows), n, hidden,
         dtype_code(dtype), _stream()), "norm_chain")
@@ -302,7 +309,7 @@ def gated_delta_rule(proj: torch.Tensor, conv_col: int, b_col: int, a_col: int, 
     _need(out.dtype == torch.float32 and out.is_contiguous() and out.shape[0] >= n and out.shape[1] == heads * vdim, "gated_delta_rule: out")
     _need(dim <= 256, f"gated_delta_rule: key size {dim} is above 256")
     prep = torch.empty((n, C), dtype=torch.float32, device=proj.device)
-    bg = torch.empty((n, 2 * heads), dtype=torch.float32, device=proj.device)
+    bg = torch.empty((n, 2 * heads + kv_heads), dtype=torch.float32, device=proj.device)
     _check(lib("recurrent").kl_gated_delta_rule(
         _ptr(proj), ctypes.c_longlong(proj.stride(0)), conv_col, b_col, a_col, _ptr(conv_weight), taps, _ptr(A_log), _ptr(dt_bias),
         _ptr(state), ctypes.c_longlong(state.stride(0)), ctypes.c_longlong(conv_off), _ptr(prep), _ptr(bg), _ptr(out),

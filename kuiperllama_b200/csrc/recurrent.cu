@@ -73,15 +73,6 @@ mingru_scan_kernel(const T* __restrict__ proj, long long ld, int z_col, int x_co
 // chunk_first[s] + c of the (A, B) arrays, which the host sizes for the step.
 constexpr int MG_CHUNK = 64;
 
-template <typename T>
-__device__ __forceinline__ void mingru_gates(const T* __restrict__ row, int z_col, int x_col, int c, float biasz, float biasx,
-                                             float& a, float& b) {
-    const float z = sigmoidf_(to_f32(row[z_col + c]) + biasz);
-    const float u = to_f32(row[x_col + c]) + biasx;
-    a = 1.0f - z;
-    b = z * (u >= 0.f ? u + 0.5f : sigmoidf_(u));
-}
-
 template <typename T, int PASS>
 __global__ void __launch_bounds__(128)
 mingru_chunk_kernel(const T* __restrict__ proj, long long ld, int z_col, int x_col, int g_col, const float* __restrict__ bz,
@@ -113,37 +104,63 @@ mingru_chunk_kernel(const T* __restrict__ proj, long long ld, int z_col, int x_c
     if (k >= n_chunks) return;
     float* e = ab + (size_t)k * 3 * width;
     const int t0 = r0 + k * MG_CHUNK, t1 = min(t0 + MG_CHUNK, r1);
-    if (PASS == 1) {
-        float A = 1.f, B = 0.f;
-        for (int r = t0; r < t1; ++r) {
-            float a, b;
-            mingru_gates(proj + (size_t)r * ld, z_col, x_col, c, biasz, biasx, a, b);
-            A *= a;
-            B = fmaf(a, B, b);
+    constexpr int U = 8;                                  // rows whose loads are in flight together
+    float A = 1.f, B = 0.f, S = PASS == 3 ? e[2 * width] : 0.f;
+    for (int r = t0; r < t1; r += U) {
+        T pz[U], px[U], pg[U];
+#pragma unroll
+        for (int k = 0; k < U; ++k) {
+            const T* row = proj + (size_t)min(r + k, t1 - 1) * ld;
+            pz[k] = row[z_col + c];
+            px[k] = row[x_col + c];
+            if (PASS == 3) pg[k] = row[g_col + c];
         }
+#pragma unroll
+        for (int k = 0; k < U; ++k) {
+            if (r + k < t1) {
+                const float z = sigmoidf_(to_f32(pz[k]) + biasz);
+                const float u = to_f32(px[k]) + biasx;
+                const float a = 1.0f - z, b = z * (u >= 0.f ? u + 0.5f : sigmoidf_(u));
+                if (PASS == 1) {
+                    A *= a;
+                    B = fmaf(a, B, b);
+                } else {
+                    S = fmaf(a, S, b);
+                    const float g = to_f32(pg[k]);
+                    out[(size_t)(r + k) * width + c] = from_f32<T>(S * (g * sigmoidf_(g)));
+                }
+            }
+        }
+    }
+    if (PASS == 1) {
         e[0] = A;
         e[width] = B;
-    } else {
-        float S = e[2 * width];
-        for (int r = t0; r < t1; ++r) {
-            const T* row = proj + (size_t)r * ld;
-            float a, b;
-            mingru_gates(row, z_col, x_col, c, biasz, biasx, a, b);
-            S = fmaf(a, S, b);
-            const float g = to_f32(row[g_col + c]);
-            out[(size_t)r * width + c] = from_f32<T>(S * (g * sigmoidf_(g)));
-        }
     }
 }
 
 // ------------------------------------------------------------------------------------------ gated delta rule
-// Step 1, one CTA per token: the short convolution and SiLU over the C = 2 G d + H dv channels of
-// q | k | v, unit length for each q and k head (q also times q_scale), and the token's beta and
-// decay per head.  The taps before the step's first token come from the slot's convolution state
-// ([taps - 1][C], entry m holding the input of time m - (taps - 1) relative to the step's start).
-//   prep [rows][C] float32: q | k | v after all that;  bg [rows][2 H]: beta | decay.
+// Step 1, one CTA per (token, item): an item is a key head g (the short convolution and SiLU over the
+// channels of q_g and k_g, unit length for both, q also times q_scale, and k_g . q_g) or a value head h
+// (convolution and SiLU over its dv channels, and the token's beta and decay for that head).  The taps
+// before the step's first token come from the slot's convolution state ([taps - 1][C], C = 2 G d + H dv,
+// entry m holding the input of time m - (taps - 1) relative to the step's start).
+//   prep [rows][C] float32: q | k | v after all that;  bg [rows][2 H + G]: beta | decay | k . q.
+constexpr int DP_THREADS = 128;
+
 template <typename T>
-__global__ void __launch_bounds__(256)
+__device__ __forceinline__ float conv_silu(const T* __restrict__ proj, long long ld, int conv_col, const float* __restrict__ taps_w,
+                                           int taps, const float* __restrict__ cs, int C, int r0, int j, int c) {
+    float acc = 0.f;
+    for (int i = 0; i < taps; ++i) {
+        const int tt = j - (taps - 1 - i);
+        const float x = tt >= 0 ? to_f32(proj[(size_t)(r0 + tt) * ld + conv_col + c]) : cs[(size_t)(taps - 1 + tt) * C + c];
+        acc = fmaf(taps_w[(size_t)c * taps + i], x, acc);
+    }
+    return acc * sigmoidf_(acc);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(DP_THREADS)
 delta_prepare_kernel(const T* __restrict__ proj, long long ld, int conv_col, int b_col, int a_col,
                      const float* __restrict__ taps_w, int taps, const float* __restrict__ A_log, const float* __restrict__ dt_bias,
                      const float* __restrict__ state, long long state_ld, long long conv_off,
@@ -151,52 +168,70 @@ delta_prepare_kernel(const T* __restrict__ proj, long long ld, int conv_col, int
                      const int* __restrict__ seq_slots, int H, int G, int d, int dv, float q_scale, float unit_eps) {
     pdl_launch_dependents();
     pdl_wait();
-    extern __shared__ float buf[];                        // [C]
-    const int s = blockIdx.y, j = blockIdx.x;
+    extern __shared__ float buf[];                        // [2 d] and 33 for the sums
+    const int s = blockIdx.y, j = blockIdx.x, item = blockIdx.z;
     const int r0 = cu_tokens[s];
     if (j >= cu_tokens[s + 1] - r0) return;
     const int row = r0 + j;
     const int C = 2 * G * d + H * dv;
     const float* cs = state + (size_t)seq_slots[s] * state_ld + conv_off;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
-        float acc = 0.f;
-        for (int i = 0; i < taps; ++i) {
-            const int tt = j - (taps - 1 - i);
-            const float x = tt >= 0 ? to_f32(proj[(size_t)(r0 + tt) * ld + conv_col + c]) : cs[(size_t)(taps - 1 + tt) * C + c];
-            acc = fmaf(taps_w[(size_t)c * taps + i], x, acc);
-        }
-        buf[c] = acc * sigmoidf_(acc);
-    }
-    __syncthreads();
     float* o = prep + (size_t)row * C;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    for (int seg = warp; seg < 2 * G; seg += nwarps) {    // q heads, then k heads
-        const float* x = buf + (size_t)seg * d;
-        float ss = 0.f;
-        for (int i = lane; i < d; i += 32) ss += x[i] * x[i];
-        ss = warp_sum(ss);
-        const float inv = (seg < G ? q_scale : 1.0f) / sqrtf(ss + unit_eps);
-        for (int i = lane; i < d; i += 32) o[(size_t)seg * d + i] = x[i] * inv;
+    float* b = bg + (size_t)row * (2 * H + G);
+    if (item >= G) {
+        const int h = item - G;
+        for (int e = threadIdx.x; e < dv; e += blockDim.x) {
+            const int c = 2 * G * d + h * dv + e;
+            o[c] = conv_silu(proj, ld, conv_col, taps_w, taps, cs, C, r0, j, c);
+        }
+        if (threadIdx.x == 0) {
+            const T* pr = proj + (size_t)row * ld;
+            b[h] = sigmoidf_(to_f32(pr[b_col + h]));
+            b[H + h] = expf(-expf(A_log[h]) * softplusf_(to_f32(pr[a_col + h]) + dt_bias[h]));
+        }
+        return;
     }
-    for (int c = 2 * G * d + threadIdx.x; c < C; c += blockDim.x) o[c] = buf[c];
-    for (int h = threadIdx.x; h < H; h += blockDim.x) {
-        const T* pr = proj + (size_t)row * ld;
-        bg[(size_t)row * 2 * H + h] = sigmoidf_(to_f32(pr[b_col + h]));
-        bg[(size_t)row * 2 * H + H + h] = expf(-expf(A_log[h]) * softplusf_(to_f32(pr[a_col + h]) + dt_bias[h]));
+    const int g = item;
+    float* scratch = buf + 2 * d;
+    float ssq = 0.f, ssk = 0.f;
+    for (int e = threadIdx.x; e < 2 * d; e += blockDim.x) {
+        const int c = e < d ? g * d + e : (G + g) * d + (e - d);
+        const float y = conv_silu(proj, ld, conv_col, taps_w, taps, cs, C, r0, j, c);
+        buf[e] = y;
+        if (e < d) ssq += y * y; else ssk += y * y;
     }
+    ssq = block_sum(ssq, scratch);
+    ssk = block_sum(ssk, scratch);
+    float kq = 0.f;
+    for (int e = threadIdx.x; e < d; e += blockDim.x) kq = fmaf(buf[e], buf[d + e], kq);
+    kq = block_sum(kq, scratch);
+    const float invq = q_scale / sqrtf(ssq + unit_eps), invk = 1.0f / sqrtf(ssk + unit_eps);
+    for (int e = threadIdx.x; e < d; e += blockDim.x) {
+        o[(size_t)g * d + e] = buf[e] * invq;
+        o[(size_t)(G + g) * d + e] = buf[d + e] * invk;
+    }
+    if (threadIdx.x == 0) b[2 * H + g] = kq * invq * invk;
 }
 
 // Step 2, the recurrence.  A column j of S (all keys' weights for value element j) never meets
 // another column, so a CTA owns some columns of one head of one sequence and walks the tokens in
 // order.  A column is cut over LPC adjacent lanes of 32 key elements each (d <= 32 LPC), kept in
-// registers; the tokens' k, q, v, beta and decay come through shared memory a tile of tokens at a time.
+// registers; the tokens' k, q, v, beta, decay and k . q come through shared memory a tile of tokens at a
+// time, the next tile on its way (cp.async) while this one is worked on.
 // The read-out after the write, o = S_new^T q, is taken from the state before it:
 //     S_new^T q = g S^T q + (k . q) u,
 // so that both products with the old state (S^T k and S^T q) run side by side and only one
 // multiply-add per element lies between one token's products and the next one's.
-// Before it starts, the first CTA of a sequence moves the convolution state on (the raw projections
-// of the step's last taps - 1 tokens; step 1 has finished with the old one).
+// Before they start, the CTAs of a sequence move the convolution state on between them (the raw
+// projections of the step's last taps - 1 tokens; step 1 has finished with the old one).
+// The slot's S is stored [H][d][dv], so that the lanes of a warp read neighbouring words.
 constexpr int DR_THREADS = 128, DR_TILE = 8, DR_DPT = 32;
+
+__device__ __forceinline__ void cp_async4(float* smem, const float* gmem) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(a), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 template <typename T, int LPC>
 __global__ void __launch_bounds__(DR_THREADS)
@@ -209,17 +244,19 @@ delta_rule_kernel(const float* __restrict__ prep, const float* __restrict__ bg, 
     constexpr int COLS = DR_THREADS / LPC;
     constexpr int DP = DR_DPT * LPC;                      // padded key size
     constexpr int DPS = (DR_DPT + 1) * LPC;               // in shared memory every part starts one bank further on
-    __shared__ float ks[DR_TILE][DPS], qs[DR_TILE][DPS], vs[DR_TILE][COLS], bs[DR_TILE], gs[DR_TILE], kqs[DR_TILE];
+    __shared__ float ks[2][DR_TILE][DPS], qs[2][DR_TILE][DPS], vs[2][DR_TILE][COLS], sc[2][DR_TILE][4];
     const int s = blockIdx.z, h = blockIdx.y;
     const int r0 = cu_tokens[s], r1 = cu_tokens[s + 1];
     if (r1 <= r0) return;
     const int slot = seq_slots[s];
     const int C = 2 * G * d + H * dv;
+    const int W = 2 * H + G;
     float* slot_state = state + (size_t)slot * state_ld;
-    if (blockIdx.x == 0 && h == 0 && taps > 1) {
+    if (taps > 1) {
         float* cs = slot_state + conv_off;
         const int n_new = r1 - r0;
-        for (int c = threadIdx.x; c < C; c += blockDim.x)
+        const int n_ctas = gridDim.x * gridDim.y, mine = blockIdx.y * gridDim.x + blockIdx.x;
+        for (int c = mine * DR_THREADS + threadIdx.x; c < C; c += n_ctas * DR_THREADS)
             for (int m = 0; m < taps - 1; ++m) {          // ascending: an old entry is read before it is overwritten
                 const int tt = n_new - (taps - 1) + m;
                 cs[(size_t)m * C + c] = tt >= 0 ? to_f32(proj[(size_t)(r0 + tt) * ld + conv_col + c]) : cs[(size_t)(n_new + m) * C + c];
@@ -230,44 +267,50 @@ delta_rule_kernel(const float* __restrict__ prep, const float* __restrict__ bg, 
     const int col = blockIdx.x * COLS + col_local;
     const bool live = col < dv;
     float S[DR_DPT];
-    float* sp = slot_state + ((size_t)h * dv + (live ? col : 0)) * d + part * DR_DPT;
+    float* sp = slot_state + ((size_t)h * d + part * DR_DPT) * dv + (live ? col : 0);
 #pragma unroll
-    for (int i = 0; i < DR_DPT; ++i) S[i] = (live && part * DR_DPT + i < d) ? sp[i] : 0.f;
+    for (int i = 0; i < DR_DPT; ++i) S[i] = (live && part * DR_DPT + i < d) ? sp[(size_t)i * dv] : 0.f;
 
-    for (int t0 = r0; t0 < r1; t0 += DR_TILE) {
+    auto fetch = [&](int b, int t0) {                     // a tile's inputs on their way into buffer b
         const int nt = min(DR_TILE, r1 - t0);
-        __syncthreads();
-        for (int e = threadIdx.x; e < nt * DP; e += blockDim.x) {
+        for (int e = threadIdx.x; e < nt * DP; e += DR_THREADS) {
             const int tt = e / DP, i = e - tt * DP;
-            const float* p = prep + (size_t)(t0 + tt) * C;
             const int at = i + i / DR_DPT;
-            ks[tt][at] = i < d ? p[(size_t)(G + g) * d + i] : 0.f;
-            qs[tt][at] = i < d ? p[(size_t)g * d + i] : 0.f;
-        }
-        for (int e = threadIdx.x; e < nt * COLS; e += blockDim.x) {
-            const int tt = e / COLS, c = e - tt * COLS;
-            const int cc = blockIdx.x * COLS + c;
-            vs[tt][c] = cc < dv ? prep[(size_t)(t0 + tt) * C + 2 * G * d + (size_t)h * dv + cc] : 0.f;
-        }
-        if (threadIdx.x < nt) {
-            bs[threadIdx.x] = bg[(size_t)(t0 + threadIdx.x) * 2 * H + h];
-            gs[threadIdx.x] = bg[(size_t)(t0 + threadIdx.x) * 2 * H + H + h];
-        }
-        {                                                  // k . q of every token of the tile, a warp each
-            const int lane = threadIdx.x & 31;
-            for (int tt = threadIdx.x >> 5; tt < nt; tt += DR_THREADS / 32) {
-                const float* p = prep + (size_t)(t0 + tt) * C;
-                float a = 0.f;
-                for (int i = lane; i < d; i += 32) a = fmaf(p[(size_t)(G + g) * d + i], p[(size_t)g * d + i], a);
-                a = warp_sum(a);
-                if (lane == 0) kqs[tt] = a;
+            const float* p = prep + (size_t)(t0 + tt) * C;
+            if (i < d) {
+                cp_async4(&ks[b][tt][at], p + (size_t)(G + g) * d + i);
+                cp_async4(&qs[b][tt][at], p + (size_t)g * d + i);
+            } else {
+                ks[b][tt][at] = 0.f;
+                qs[b][tt][at] = 0.f;
             }
         }
+        for (int e = threadIdx.x; e < nt * COLS; e += DR_THREADS) {
+            const int tt = e / COLS, c = e - tt * COLS;
+            const int cc = blockIdx.x * COLS + c;
+            if (cc < dv) cp_async4(&vs[b][tt][c], prep + (size_t)(t0 + tt) * C + 2 * G * d + (size_t)h * dv + cc);
+            else vs[b][tt][c] = 0.f;
+        }
+        if (threadIdx.x < nt) {
+            const float* p = bg + (size_t)(t0 + threadIdx.x) * W;
+            cp_async4(&sc[b][threadIdx.x][0], p + h);
+            cp_async4(&sc[b][threadIdx.x][1], p + H + h);
+            cp_async4(&sc[b][threadIdx.x][2], p + 2 * H + g);
+        }
+        cp_async_commit();
+    };
+
+    fetch(0, r0);
+    int b = 0;
+    for (int t0 = r0; t0 < r1; t0 += DR_TILE, b ^= 1) {
+        const int nt = min(DR_TILE, r1 - t0);
+        if (t0 + DR_TILE < r1) { fetch(b ^ 1, t0 + DR_TILE); cp_async_wait<1>(); }
+        else cp_async_wait<0>();
         __syncthreads();
         for (int tt = 0; tt < nt; ++tt) {
-            const float* kk = &ks[tt][part * (DR_DPT + 1)];
-            const float* qq = &qs[tt][part * (DR_DPT + 1)];
-            const float decay = gs[tt], beta = bs[tt];
+            const float* kk = &ks[b][tt][part * (DR_DPT + 1)];
+            const float* qq = &qs[b][tt][part * (DR_DPT + 1)];
+            const float beta = sc[b][tt][0], decay = sc[b][tt][1], kq = sc[b][tt][2];
             float sk[4] = {0.f, 0.f, 0.f, 0.f}, sq[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int i = 0; i < DR_DPT; ++i) {
@@ -280,16 +323,17 @@ delta_rule_kernel(const float* __restrict__ prep, const float* __restrict__ bg, 
                 skt += __shfl_xor_sync(0xffffffffu, skt, o);
                 sqt += __shfl_xor_sync(0xffffffffu, sqt, o);
             }
-            const float u = beta * (vs[tt][col_local] - decay * skt);
+            const float u = beta * (vs[b][tt][col_local] - decay * skt);
 #pragma unroll
             for (int i = 0; i < DR_DPT; ++i) S[i] = fmaf(kk[i], u, decay * S[i]);
-            if (live && part == 0) out[((size_t)(t0 + tt) * H + h) * dv + col] = fmaf(kqs[tt], u, decay * sqt);
+            if (live && part == 0) out[((size_t)(t0 + tt) * H + h) * dv + col] = fmaf(kq, u, decay * sqt);
         }
+        __syncthreads();                                   // the buffer is free for the tile after the next
     }
     if (live) {
 #pragma unroll
         for (int i = 0; i < DR_DPT; ++i)
-            if (part * DR_DPT + i < d) sp[i] = S[i];
+            if (part * DR_DPT + i < d) sp[(size_t)i * dv] = S[i];
     }
 }
 
@@ -336,36 +380,34 @@ KL_API int kl_mingru_scan(const void* proj, long long ld, int z_col, int x_col, 
 
 // The two steps of the gated delta rule.  proj: compute dtype [rows, ld] with q | k | v at conv_col
 // (C = 2 G d + H dv columns), beta's and the decay's projections at b_col and a_col (H each).
-// state: float32 [slots][state_ld]: S as [H][dv][d] at 0, the convolution state [taps - 1][C] at conv_off.
-// prep [rows, C], bg [rows, 2 H], out [rows, H * dv]: float32.  max_new: no sequence brings more rows.
+// state: float32 [slots][state_ld]: S as [H][d][dv] at 0, the convolution state [taps - 1][C] at conv_off.
+// prep [rows, C], bg [rows, 2 H + G], out [rows, H * dv]: float32.  max_new: no sequence brings more rows.
 KL_API int kl_gated_delta_rule(const void* proj, long long ld, int conv_col, int b_col, int a_col, const float* taps_w, int taps,
                                const float* A_log, const float* dt_bias, float* state, long long state_ld, long long conv_off,
                                float* prep, float* bg, float* out, const int* cu_tokens, const int* seq_slots, int n_seqs,
                                int max_new, int H, int G, int d, int dv, float q_scale, float unit_eps, int dtype,
                                cudaStream_t stream) {
     if (n_seqs <= 0 || max_new <= 0) return KL_OK;
-    if (H <= 0 || G <= 0 || H % G || d <= 0 || dv <= 0 || taps < 1 || d > DR_DPT * 8 || n_seqs > 65535) return KL_ERR_BAD_SIZE;
-    const int C = 2 * G * d + H * dv;
-    const size_t smem = (size_t)C * sizeof(float);
-    if (smem > 200 * 1024) return KL_ERR_BAD_SIZE;
+    if (H <= 0 || G <= 0 || H % G || d <= 0 || dv <= 0 || taps < 1 || d > DR_DPT * 8 || n_seqs > 65535 || G + H > 65535) return KL_ERR_BAD_SIZE;
+    const size_t smem = (size_t)(2 * d + 33) * sizeof(float);
     const int lpc = d <= 32 ? 1 : d <= 64 ? 2 : d <= 128 ? 4 : 8;
-    const dim3 grid1(max_new, n_seqs);
+    const dim3 grid1(max_new, n_seqs, G + H);
     const dim3 grid2((dv + DR_THREADS / lpc - 1) / (DR_THREADS / lpc), H, n_seqs);
+    if (grid2.y > 65535) return KL_ERR_BAD_SIZE;
+#define KL_DR(T, L) launch_kernel(delta_rule_kernel<T, L>, grid2, DR_THREADS, 0, stream, (const float*)prep, (const float*)bg, (const T*)proj, ld, \
+                                  conv_col, taps, state, state_ld, conv_off, out, cu_tokens, seq_slots, H, G, d, dv)
 #define KL_DELTA(T)                                                                                                          \
     do {                                                                                                                     \
-        if (smem > 48 * 1024) KL_CUDA(cudaFuncSetAttribute(delta_prepare_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        launch_kernel(delta_prepare_kernel<T>, grid1, 256, smem, stream, (const T*)proj, ld, conv_col, b_col, a_col, taps_w, taps, A_log, \
+        launch_kernel(delta_prepare_kernel<T>, grid1, DP_THREADS, smem, stream, (const T*)proj, ld, conv_col, b_col, a_col, taps_w, taps, A_log, \
                       dt_bias, (const float*)state, state_ld, conv_off, prep, bg, cu_tokens, seq_slots, H, G, d, dv, q_scale, unit_eps); \
         KL_LAUNCH_CHECK();                                                                                                   \
-        if (lpc == 1) launch_kernel(delta_rule_kernel<T, 1>, grid2, DR_THREADS, 0, stream, (const float*)prep, (const float*)bg, (const T*)proj, ld, conv_col, taps, state, state_ld, conv_off, out, cu_tokens, seq_slots, H, G, d, dv); \
-        else if (lpc == 2) launch_kernel(delta_rule_kernel<T, 2>, grid2, DR_THREADS, 0, stream, (const float*)prep, (const float*)bg, (const T*)proj, ld, conv_col, taps, state, state_ld, conv_off, out, cu_tokens, seq_slots, H, G, d, dv); \
-        else if (lpc == 4) launch_kernel(delta_rule_kernel<T, 4>, grid2, DR_THREADS, 0, stream, (const float*)prep, (const float*)bg, (const T*)proj, ld, conv_col, taps, state, state_ld, conv_off, out, cu_tokens, seq_slots, H, G, d, dv); \
-        else launch_kernel(delta_rule_kernel<T, 8>, grid2, DR_THREADS, 0, stream, (const float*)prep, (const float*)bg, (const T*)proj, ld, conv_col, taps, state, state_ld, conv_off, out, cu_tokens, seq_slots, H, G, d, dv); \
+        if (lpc == 1) KL_DR(T, 1); else if (lpc == 2) KL_DR(T, 2); else if (lpc == 4) KL_DR(T, 4); else KL_DR(T, 8);          \
     } while (0)
     if (dtype == KL_F32) KL_DELTA(float);
     else if (dtype == KL_BF16) KL_DELTA(bf16);
     else return KL_ERR_BAD_DTYPE;
 #undef KL_DELTA
+#undef KL_DR
     KL_LAUNCH_CHECK();
     return KL_OK;
 }

@@ -64,9 +64,11 @@ class AttentionMixer(Mixer):
         self.values_are_keys = spec.get("values", "own") == "keys"
         self.gated = bool(n.get("g"))
         if self.values_are_keys or self.gated:
-            self.inputs = StackedInput(runtime)               # q | k | (v) | (g), then whatever rides along
-            for k in ("q", "k") + (() if self.values_are_keys else ("v",)) + (("g",) if self.gated else ()):
-                self.inputs.add(k, tensors[prefix + n[k]])
+            self.inputs = StackedInput(runtime)               # q | k | (v) as the leading columns, then g, then whatever rides along
+            self.inputs.add("qkv", torch.cat([tensors[prefix + n[k]].to(device=dev, dtype=dt)
+                                              for k in ("q", "k") + (() if self.values_are_keys else ("v",))], dim=0))
+            if self.gated:
+                self.inputs.add("g", tensors[prefix + n["g"]])
         else:
             stacked = torch.cat([tensors[prefix + n[k]].to(device=dev, dtype=dt) for k in ("q", "k", "v")], dim=0)
             self.qkv = Linear(stacked, runtime)
@@ -94,7 +96,7 @@ class AttentionMixer(Mixer):
                       self.scale, int(self.window or 0))
         if self.gated:
             ops.sigmoid_gate(attn, self.inputs.view("g"))
-        return self.o.forward(attn)
+        return self.o.forward(attn, allow_partials=True)
 
     def forward(self, x: torch.Tensor, step: StepContext, cache: CacheView) -> torch.Tensor:
         if self.values_are_keys or self.gated:

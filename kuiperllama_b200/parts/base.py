@@ -119,7 +119,7 @@ class PostNormed:
     d = value * sigmoid(gate + gate_bias) where a gate is given, then d = norm(d) where a norm is
     given, then the 32-bit sum.  The norm that reads the stream next does all of it in its own
     kernel (``ops.norm_chain``), as it adds a plain pending delta."""
-    value: torch.Tensor                       # [n_tokens, hidden], compute dtype, any row stride
+    value: torch.Tensor                       # [n_tokens, hidden], compute dtype, any row stride; or float32 pieces [S, n_tokens, hidden]
     gate: Optional[torch.Tensor] = None       # [n_tokens, hidden] pre-activation, compute dtype, any row stride
     gate_bias: Optional[torch.Tensor] = None  # float32 [hidden]
     norm: Optional["Norm"] = None             # applied to the gated value; has weight, bias, eps, kind

@@ -73,9 +73,7 @@ class SandwichBlock:
 
     @staticmethod
     def _result(y, h, gate: Optional[ResidualGate], norm: Optional[Norm]) -> PostNormed:
-        if y.dim() == 3:                                 # float32 pieces of a product: their sum, once
-            y = y.sum(dim=0).to(h.dtype)
-        if gate is None:
+        if gate is None:                                 # y may be float32 pieces of a product: the norm kernel adds them
             return PostNormed(y, norm=norm)
         return PostNormed(y, gate=gate.pre_activation(h), gate_bias=gate.bias, norm=norm)
 

@@ -52,4 +52,4 @@ class DenseFeedForward(FeedForward):
         self.inputs.forward(x)
         act = torch.empty((x.shape[0], self.inter), dtype=self.runtime.dtype, device=x.device)
         ops.activation(self.inputs.view("up"), act, self.activation, self.params)
-        return self.down.forward(act)
+        return self.down.forward(act, allow_partials=True)

@@ -60,12 +60,16 @@ class StackedInput:
     output axis once (at the first ``forward``), and every projection is a column slice of the
     result.  A part that keeps its input projections here lets others (a residual gate that reads
     the same rows) ``add`` theirs, which saves a product each; kernels take the slices by column
-    offset and the matrix's row stride.  (KuiperLLama runs wq, wk, wv as three products,
+    offset and the matrix's row stride.  Every projection starts at a multiple of ``ALIGN`` columns
+    and so does every row (rows of zeros fill the gaps), so that slices of sizes like 2 or 3 heads
+    leave the others on the 16-byte boundaries that vector loads and the tensor-core kernels want.  (KuiperLLama runs wq, wk, wv as three products,
     kuiper/source/model/llama3.cpp:610-639.)"""
+
+    ALIGN = 8
 
     def __init__(self, runtime: Runtime):
         self.runtime = runtime
-        self._pieces = []                  # (name, weight) until the first forward
+        self._pieces = []                  # (name, weight) until the first forward; name None: a gap of zeros
         self.columns = {}                  # name -> (first column, width)
         self.linear: Optional[Linear] = None
         self.total = 0
@@ -77,15 +81,24 @@ class StackedInput:
         if name in self.columns:
             raise ValueError(f"projection {name!r} is already stacked")
         w = weight.to(device=self.runtime.device, dtype=self.runtime.dtype)
+        self._pad()
         self._pieces.append((name, w))
         self.columns[name] = (self.total, w.shape[0])
         self.total += w.shape[0]
+
+    def _pad(self) -> None:
+        gap = -self.total % self.ALIGN
+        if gap and self._pieces:
+            like = self._pieces[0][1]
+            self._pieces.append((None, torch.zeros((gap, like.shape[1]), dtype=like.dtype, device=like.device)))
+            self.total += gap
 
     def column(self, name: str) -> int:
         return self.columns[name][0]
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self.linear is None:
+            self._pad()
             self.linear = Linear(torch.cat([w for _, w in self._pieces], dim=0), self.runtime)
             self._pieces = []
         self.last = self.linear.forward(x)

@@ -55,9 +55,7 @@ def chain_forward(norm: Norm, residual: torch.Tensor, delta, rows: Optional[torc
         if delta.norm is not None:
             post = (delta.norm.weight, delta.norm.bias, delta.norm.eps, delta.norm.kind)
     elif delta is not None:
-        if delta.dim() == 3:                                       # float32 pieces of a product: their sum, once
-            delta = delta.sum(dim=0).to(norm.runtime.dtype)
-        value = delta
+        value = delta                                              # rows, or float32 pieces of a product
     ops.norm_chain(residual, value, out, norm.weight, norm.bias, norm.eps, norm.kind, gate=gate, gate_bias=gate_bias,
                    post=post, rows=rows)
     return out

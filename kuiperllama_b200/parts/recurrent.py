@@ -58,7 +58,7 @@ class MinGRUMixer(Mixer):
         make = torch.empty if step.n_tokens == step.n_seqs else torch.zeros
         mixed = make((step.n_tokens, self.width), dtype=self.runtime.dtype, device=x.device)
         ops.mingru_scan(proj, col("z"), col("x"), col("g"), self.bias_z, self.bias_x, cache.state, mixed, step, self.width)
-        return self.o.forward(mixed)
+        return self.o.forward(mixed, allow_partials=True)
 
 
 @register_mixer("gated_delta")
@@ -72,7 +72,7 @@ class GatedDeltaMixer(Mixer):
         S <- decay S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
 
     and out = Wo (o / rms(o) * w_norm * silu(Wg n)), the RMS over each head's dv values.  The slot's
-    state is float32: S as [H, dv, d], then the last conv - 1 inputs of the convolution.  All of
+    state is float32: S as [H, d, dv], then the last conv - 1 inputs of the convolution.  All of
     q, k, v, beta, decay and g come from one product.  Spec: ``hidden_size``, ``heads``,
     ``kv_heads``, ``dim``, ``vdim``, ``conv``, ``norm_eps``, ``unit_eps``, ``q_scale`` and ``names``.
     KuiperLLama has no recurrent mixer (its mixer is mha_kernel.cu:61,74-106)."""
@@ -106,7 +106,10 @@ class GatedDeltaMixer(Mixer):
         self.q_scale = float(spec["q_scale"])
         n = spec["names"]
         self.inputs = StackedInput(runtime)
-        for k in ("q", "k", "v", "beta", "a", "g"):
+        dev, dt = runtime.device, runtime.dtype
+        # q | k | v as one piece: the convolution runs over their channels as one range
+        self.inputs.add("qkv", torch.cat([tensors[prefix + n[k]].to(device=dev, dtype=dt) for k in ("q", "k", "v")], dim=0))
+        for k in ("g", "beta", "a"):
             self.inputs.add(k, tensors[prefix + n[k]])
         self.o = Linear(tensors[prefix + n["o"]], runtime)
         f32 = lambda name: tensors[prefix + name].to(device=runtime.device, dtype=torch.float32).contiguous()
@@ -127,8 +130,8 @@ class GatedDeltaMixer(Mixer):
         # rows that belong to no sequence (a small step's padding) are not written by the scan: keep them defined
         make = torch.empty if n == step.n_seqs else torch.zeros
         o = make((n, self.H * self.dv), dtype=torch.float32, device=x.device)
-        ops.gated_delta_rule(proj, col("q"), col("beta"), col("a"), self.conv_weight, self.A_log, self.dt_bias, cache.state,
+        ops.gated_delta_rule(proj, col("qkv"), col("beta"), col("a"), self.conv_weight, self.A_log, self.dt_bias, cache.state,
                              self.conv_off, o, step, self.H, self.G, self.d, self.dv, self.q_scale, self.unit_eps)
         gated = torch.empty((n, self.H * self.dv), dtype=self.runtime.dtype, device=x.device)
         ops.head_rmsnorm_gate(o, self.inputs.view("g"), self.norm_weight, gated, self.H, self.dv, self.norm_eps)
-        return self.o.forward(gated)
+        return self.o.forward(gated, allow_partials=True)

@@ -88,13 +88,15 @@ def test_one_mechanism_alone(models, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_kernels_against_the_plain_functions(dtype):
-    """The new kernels one by one on random inputs: norm chain, activation, gates, per-head norm."""
+@pytest.mark.parametrize("hid", [100, 99, 1536])
+def test_norm_chain_against_the_plain_functions(dtype, hid):
+    """gate, norm after, 32-bit sum, norm before, as one kernel: rows on 16-byte boundaries (the form that
+    keeps a row in registers), rows on none (hid 99), the result given as rows or as float32 pieces."""
     from kuiperllama_b200.csrc import ops
     dt = getattr(torch, dtype)
     dev = "cuda:0"
     g = torch.Generator().manual_seed(5)
-    n, hid = 37, 100
+    n = 37
     rnd = lambda *s: torch.randn(*s, generator=g)
     x, d, gate = rnd(n, hid) * 3, rnd(n, hid).to(dt), rnd(n, hid).to(dt)
     gb, pw, pb, w, b = rnd(hid), 1 + 0.3 * rnd(hid), rnd(hid), 1 + 0.3 * rnd(hid), rnd(hid)
@@ -116,11 +118,38 @@ def test_kernels_against_the_plain_functions(dtype):
                        post=(pw.to(dev), pb.to(dev), 1e-5, kind), rows=rows)
         assert torch.equal(res2.cpu(), x), "with rows the stream stays as it is"
         assert torch.equal(out2, out[rows.long()])
+        # the same result handed over as three float32 pieces
+        pieces = torch.stack([d.float() * 0.5, d.float() * 0.25, d.float() * 0.25]).to(dev).contiguous()
+        res3, out3 = x.to(dev).clone(), torch.empty(n, hid, dtype=dt, device=dev)
+        ops.norm_chain(res3, pieces, out3, w.to(dev), b.to(dev), 2e-6, kind, gate=wide[:, :hid], gate_bias=gb.to(dev),
+                       post=(pw.to(dev), pb.to(dev), 1e-5, kind))
+        assert torch.allclose(res3, res, atol=1e-5, rtol=1e-5) and torch.allclose(out3.float(), out.float(), atol=tol, rtol=tol)
+        # nothing to add: the norm of the stream alone; and the sum alone
+        res4, out4 = x.to(dev).clone(), torch.empty(n, hid, dtype=dt, device=dev)
+        ops.norm_chain(res4, None, out4, w.to(dev), b.to(dev), 2e-6, kind)
+        assert torch.equal(res4.cpu(), x) and torch.allclose(out4.cpu().double(), norm(x.double(), w.double(), b.double(), 2e-6), atol=tol * 4, rtol=tol)
+        ops.norm_chain(res4, wide[:, hid:], None, None, None, 0.0, kind)
+        assert torch.allclose(res4.cpu().double(), x.double() + d.double(), atol=1e-5, rtol=1e-5)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_kernels_against_the_plain_functions(dtype):
+    """The other new kernels one by one on random inputs: activations, the sigmoid gate, the per-head norm."""
+    from kuiperllama_b200.csrc import ops
+    dt = getattr(torch, dtype)
+    dev = "cuda:0"
+    g = torch.Generator().manual_seed(6)
+    n, hid = 37, 100
+    rnd = lambda *s: torch.randn(*s, generator=g)
+    tol = 1e-5 if dtype == "float32" else 2e-2
     z = (rnd(n, hid) * 2).to(dt)
     params = torch.tensor([float(P.softplus(torch.tensor(0.3, dtype=P.F))), 0.5 + float(P.softplus(torch.tensor(-0.7, dtype=P.F)))])
     got = torch.empty(n, hid, dtype=dt, device=dev)
     ops.activation(z.to(dev), got, "xielu", params.to(dev))
     assert torch.allclose(got.cpu().double(), P.xielu(z.double(), 0.3, -0.7), atol=tol, rtol=tol)
+    odd = torch.empty(n, hid - 1, dtype=dt, device=dev)                 # a width that takes the element-by-element form
+    ops.activation(z.to(dev)[:, 1:], odd, "xielu", params.to(dev))
+    assert torch.equal(odd, got[:, 1:])
     ops.activation(z.to(dev), got, "gelu_tanh")
     zz = z.double()
     assert torch.allclose(got.cpu().double(), 0.5 * zz * (1 + torch.tanh(math.sqrt(2 / math.pi) * (zz + 0.044715 * zz ** 3))), atol=tol, rtol=tol)
