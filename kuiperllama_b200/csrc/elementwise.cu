@@ -10,10 +10,13 @@ enum : int { ACT_XIELU = 0, ACT_GELU_TANH = 1, ACT_SILU = 2 };
 
 // xIELU with a_pos = softplus(p) and a_neg = 1/2 + softplus(q) (both made at load, params[0..1]):
 //   z > 0:  a_pos z^2 + z / 2          z <= 0:  a_neg (exp(z) - 1 - z) + z / 2
+// FAST (a result that is rounded to bfloat16): exp(z) - 1 from the fast exponential; its absolute error near
+// zero, 1e-7, stands beside z / 2 and is far below that format's step.
+template <bool FAST>
 __device__ __forceinline__ float activate(float z, int kind, float a_pos, float a_neg) {
-    if (kind == ACT_XIELU) return z > 0.f ? a_pos * z * z + 0.5f * z : a_neg * (expm1f(z) - z) + 0.5f * z;
+    if (kind == ACT_XIELU) return z > 0.f ? a_pos * z * z + 0.5f * z : a_neg * ((FAST ? __expf(z) - 1.0f : expm1f(z)) - z) + 0.5f * z;
     if (kind == ACT_GELU_TANH) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
-    return z / (1.0f + expf(-z));
+    return z / (1.0f + (FAST ? __expf(-z) : expf(-z)));
 }
 
 template <typename T>
@@ -26,7 +29,7 @@ __global__ void activation_kernel(const T* __restrict__ x, long long ld_x, T* __
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / n;
         const int i = (int)(idx - t * n);
-        out[t * ld_out + i] = from_f32<T>(activate(to_f32(x[t * ld_x + i]), kind, a_pos, a_neg));
+        out[t * ld_out + i] = from_f32<T>(activate<sizeof(T) == 2>(to_f32(x[t * ld_x + i]), kind, a_pos, a_neg));
     }
 }
 
@@ -46,7 +49,7 @@ __global__ void activation_vec_kernel(const T* __restrict__ x, long long ld_x, T
         uint4 raw = *reinterpret_cast<const uint4*>(x + t * ld_x + i);
         T* e = reinterpret_cast<T*>(&raw);
 #pragma unroll
-        for (int k = 0; k < V; ++k) e[k] = from_f32<T>(activate(to_f32(e[k]), kind, a_pos, a_neg));
+        for (int k = 0; k < V; ++k) e[k] = from_f32<T>(activate<sizeof(T) == 2>(to_f32(e[k]), kind, a_pos, a_neg));
         *reinterpret_cast<uint4*>(out + t * ld_out + i) = raw;
     }
 }

@@ -65,6 +65,16 @@ template <> struct Vec4<bf16> {
     }
 };
 
+// Sum over the CTA with one barrier: every warp adds up all warps' partial sums itself.  `scratch` (32
+// floats) must not be written again before every warp has read it, so each call of a kernel gets its own.
+__device__ __forceinline__ float block_sum_once(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    return warp_sum(lane < nwarps ? scratch[lane] : 0.f);
+}
+
 // One norm over a row that lies in registers, VPT float4 per thread (lanes beyond the row hold zeros and
 // stay out of the sums).
 template <int THREADS, int VPT>
@@ -75,7 +85,7 @@ __device__ __forceinline__ void norm_in_registers(float4 (&v)[VPT], int n4, int 
         float s = 0.f;
 #pragma unroll
         for (int j = 0; j < VPT; ++j) s += (v[j].x + v[j].y) + (v[j].z + v[j].w);
-        mean = block_sum(s, scratch) / (float)n;
+        mean = block_sum_once(s, scratch) / (float)n;
     }
     float ss = 0.f;
 #pragma unroll
@@ -85,7 +95,7 @@ __device__ __forceinline__ void norm_in_registers(float4 (&v)[VPT], int n4, int 
             ss += (a * a + c * c) + (e * e + f * f);
         }
     }
-    ss = block_sum(ss, scratch);
+    ss = block_sum_once(ss, scratch + 32);
     const float inv = 1.0f / sqrtf(ss / (float)n + eps);
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
@@ -116,7 +126,7 @@ norm_chain_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                       T* __restrict__ out, const int* __restrict__ rows, int hidden) {
     pdl_launch_dependents();
     pdl_wait();
-    __shared__ float scratch[33];
+    __shared__ float scratch[4 * 32];                   // a row of its own for each of the four sums
     const int r = blockIdx.x;
     const int s = rows ? rows[r] : r;
     const int n4 = hidden >> 2;
@@ -131,9 +141,16 @@ norm_chain_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta,
         if (i4 < n4) {
             xr[j] = *reinterpret_cast<const float4*>(x + 4 * i4);
             if (delta != nullptr) v[j] = Vec4<T>::load(delta + (size_t)s * delta_ld + 4 * i4);
-            for (int z = 0; z < n_partials; ++z) {
-                const float4 p = *reinterpret_cast<const float4*>(partials + (size_t)z * partial_stride + (size_t)s * hidden + 4 * i4);
-                v[j].x += p.x; v[j].y += p.y; v[j].z += p.z; v[j].w += p.w;
+            for (int z0 = 0; z0 < n_partials; z0 += 8) {          // eight pieces on their way at a time, added in ascending order
+                float4 p[8];
+#pragma unroll
+                for (int zz = 0; zz < 8; ++zz)
+                    p[zz] = z0 + zz < n_partials
+                                ? *reinterpret_cast<const float4*>(partials + (size_t)(z0 + zz) * partial_stride + (size_t)s * hidden + 4 * i4)
+                                : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int zz = 0; zz < 8; ++zz)
+                    if (z0 + zz < n_partials) { v[j].x += p[zz].x; v[j].y += p[zz].y; v[j].z += p[zz].z; v[j].w += p[zz].w; }
             }
             if (gate != nullptr) {
                 float4 a = Vec4<T>::load(gate + (size_t)s * gate_ld + 4 * i4);
@@ -159,7 +176,7 @@ norm_chain_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta,
         for (int j = 0; j < VPT; ++j) v[j] = xr[j];
     }
     if (out == nullptr) return;
-    norm_in_registers<THREADS, VPT>(v, n4, hidden, w, b, eps, kind, scratch);
+    norm_in_registers<THREADS, VPT>(v, n4, hidden, w, b, eps, kind, scratch + 64);
     T* o = out + (size_t)r * hidden;
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {

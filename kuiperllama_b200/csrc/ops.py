@@ -262,7 +262,7 @@ def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor) -> None:
 
 # --------------------------------------------------------------------------- recurrent mixers
 
-MINGRU_CHUNK = 64              # equals MG_CHUNK in recurrent.cu
+MINGRU_CHUNK = 32              # equals MG_CHUNK in recurrent.cu
 MINGRU_CHUNKED_FROM = 256      # tokens of the longest sequence from which a step takes the chunked scan
 
 
@@ -276,7 +276,7 @@ def mingru_scan(proj: torch.Tensor, z_col: int, x_col: int, g_col: int, bias_z: 
     _need(out.is_contiguous() and out.dtype == proj.dtype and out.shape[1] == width and out.shape[0] >= step.n_tokens, "mingru_scan: out")
     for b in (bias_z, bias_x):
         _need(b is None or (b.dtype == torch.float32 and b.numel() == width and b.is_contiguous()), "mingru_scan: bias")
-    # Steps with long sequences run in chunks of 64 tokens (three passes, every chunk at once); a thread that
+    # Steps with long sequences run in chunks of 32 tokens (three passes, every chunk at once); a thread that
     # walks its channel alone is faster while a sequence brings few chunks.
     scratch, launches = None, 1
     if step.max_new >= MINGRU_CHUNKED_FROM:

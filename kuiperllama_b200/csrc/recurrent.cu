@@ -71,7 +71,7 @@ mingru_scan_kernel(const T* __restrict__ proj, long long ld, int z_col, int x_co
 // after the step.  Pass 3, a thread per (chunk, channel): the chunk again from its true start, writing
 // out.  Chunks are counted per sequence from the step's first token; chunk c of sequence s is entry
 // chunk_first[s] + c of the (A, B) arrays, which the host sizes for the step.
-constexpr int MG_CHUNK = 64;
+constexpr int MG_CHUNK = 32;
 
 template <typename T, int PASS>
 __global__ void __launch_bounds__(128)
@@ -92,10 +92,22 @@ mingru_chunk_kernel(const T* __restrict__ proj, long long ld, int z_col, int x_c
     if (PASS == 2) {
         float* st = state + (size_t)seq_slots[s] * state_ld + c;
         float S = *st;
-        for (int k = 0; k < n_chunks; ++k) {
-            float* e = ab + (size_t)k * 3 * width;
-            e[2 * width] = S;
-            S = fmaf(e[0], S, e[width]);
+        constexpr int U2 = 8;                             // chunks whose (A, B) are in flight together
+        for (int k0 = 0; k0 < n_chunks; k0 += U2) {
+            float A[U2], B[U2];
+#pragma unroll
+            for (int k = 0; k < U2; ++k) {
+                const float* e = ab + (size_t)min(k0 + k, n_chunks - 1) * 3 * width;
+                A[k] = e[0];
+                B[k] = e[width];
+            }
+#pragma unroll
+            for (int k = 0; k < U2; ++k) {
+                if (k0 + k < n_chunks) {
+                    ab[(size_t)(k0 + k) * 3 * width + 2 * width] = S;
+                    S = fmaf(A[k], S, B[k]);
+                }
+            }
         }
         if (n_chunks > 0) *st = S;
         return;
@@ -214,7 +226,8 @@ delta_prepare_kernel(const T* __restrict__ proj, long long ld, int conv_col, int
 
 // Step 2, the recurrence.  A column j of S (all keys' weights for value element j) never meets
 // another column, so a CTA owns some columns of one head of one sequence and walks the tokens in
-// order.  A column is cut over LPC adjacent lanes of 32 key elements each (d <= 32 LPC), kept in
+// order.  A column is cut over LPC adjacent lanes of DPT (32, or 16 where the step has few CTAs
+// otherwise) key elements each (d <= DPT LPC), kept in
 // registers; the tokens' k, q, v, beta, decay and k . q come through shared memory a tile of tokens at a
 // time, the next tile on its way (cp.async) while this one is worked on.
 // The read-out after the write, o = S_new^T q, is taken from the state before it:
@@ -224,16 +237,20 @@ delta_prepare_kernel(const T* __restrict__ proj, long long ld, int conv_col, int
 // Before they start, the CTAs of a sequence move the convolution state on between them (the raw
 // projections of the step's last taps - 1 tokens; step 1 has finished with the old one).
 // The slot's S is stored [H][d][dv], so that the lanes of a warp read neighbouring words.
-constexpr int DR_THREADS = 128, DR_TILE = 8, DR_DPT = 32;
+constexpr int DR_THREADS = 128, DR_TILE = 8;
 
 __device__ __forceinline__ void cp_async4(float* smem, const float* gmem) {
     const unsigned a = (unsigned)__cvta_generic_to_shared(smem);
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(a), "l"(gmem) : "memory");
 }
+__device__ __forceinline__ void cp_async16(float* smem, const float* gmem) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(a), "l"(gmem) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-template <typename T, int LPC>
+template <typename T, int LPC, int DR_DPT>
 __global__ void __launch_bounds__(DR_THREADS)
 delta_rule_kernel(const float* __restrict__ prep, const float* __restrict__ bg, const T* __restrict__ proj, long long ld,
                   int conv_col, int taps, float* __restrict__ state, long long state_ld, long long conv_off,
@@ -243,8 +260,9 @@ delta_rule_kernel(const float* __restrict__ prep, const float* __restrict__ bg, 
     pdl_wait();
     constexpr int COLS = DR_THREADS / LPC;
     constexpr int DP = DR_DPT * LPC;                      // padded key size
-    constexpr int DPS = (DR_DPT + 1) * LPC;               // in shared memory every part starts one bank further on
-    __shared__ float ks[2][DR_TILE][DPS], qs[2][DR_TILE][DPS], vs[2][DR_TILE][COLS], sc[2][DR_TILE][4];
+    constexpr int PS = DR_DPT + 4;                        // in shared memory every part starts four banks further on: 16-byte reads without conflicts
+    constexpr int DPS = PS * LPC;
+    __shared__ __align__(16) float ks[2][DR_TILE][DPS], qs[2][DR_TILE][DPS], vs[2][DR_TILE][COLS], sc[2][DR_TILE][4];
     const int s = blockIdx.z, h = blockIdx.y;
     const int r0 = cu_tokens[s], r1 = cu_tokens[s + 1];
     if (r1 <= r0) return;
@@ -271,18 +289,34 @@ delta_rule_kernel(const float* __restrict__ prep, const float* __restrict__ bg, 
 #pragma unroll
     for (int i = 0; i < DR_DPT; ++i) S[i] = (live && part * DR_DPT + i < d) ? sp[(size_t)i * dv] : 0.f;
 
+    const bool vec = ((d | dv) & 3) == 0 && (((uintptr_t)prep) & 15) == 0;     // rows of prep and the heads in them on 16-byte boundaries
     auto fetch = [&](int b, int t0) {                     // a tile's inputs on their way into buffer b
         const int nt = min(DR_TILE, r1 - t0);
-        for (int e = threadIdx.x; e < nt * DP; e += DR_THREADS) {
-            const int tt = e / DP, i = e - tt * DP;
-            const int at = i + i / DR_DPT;
-            const float* p = prep + (size_t)(t0 + tt) * C;
-            if (i < d) {
-                cp_async4(&ks[b][tt][at], p + (size_t)(G + g) * d + i);
-                cp_async4(&qs[b][tt][at], p + (size_t)g * d + i);
-            } else {
-                ks[b][tt][at] = 0.f;
-                qs[b][tt][at] = 0.f;
+        if (vec) {
+            for (int e = threadIdx.x; e < nt * (DP / 4); e += DR_THREADS) {
+                const int tt = e / (DP / 4), i = (e - tt * (DP / 4)) * 4;
+                const int at = (i / DR_DPT) * PS + i % DR_DPT;
+                const float* p = prep + (size_t)(t0 + tt) * C;
+                if (i < d) {
+                    cp_async16(&ks[b][tt][at], p + (size_t)(G + g) * d + i);
+                    cp_async16(&qs[b][tt][at], p + (size_t)g * d + i);
+                } else {
+                    *reinterpret_cast<float4*>(&ks[b][tt][at]) = make_float4(0.f, 0.f, 0.f, 0.f);
+                    *reinterpret_cast<float4*>(&qs[b][tt][at]) = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            }
+        } else {
+            for (int e = threadIdx.x; e < nt * DP; e += DR_THREADS) {
+                const int tt = e / DP, i = e - tt * DP;
+                const int at = (i / DR_DPT) * PS + i % DR_DPT;
+                const float* p = prep + (size_t)(t0 + tt) * C;
+                if (i < d) {
+                    cp_async4(&ks[b][tt][at], p + (size_t)(G + g) * d + i);
+                    cp_async4(&qs[b][tt][at], p + (size_t)g * d + i);
+                } else {
+                    ks[b][tt][at] = 0.f;
+                    qs[b][tt][at] = 0.f;
+                }
             }
         }
         for (int e = threadIdx.x; e < nt * COLS; e += DR_THREADS) {
@@ -308,8 +342,12 @@ delta_rule_kernel(const float* __restrict__ prep, const float* __restrict__ bg, 
         else cp_async_wait<0>();
         __syncthreads();
         for (int tt = 0; tt < nt; ++tt) {
-            const float* kk = &ks[b][tt][part * (DR_DPT + 1)];
-            const float* qq = &qs[b][tt][part * (DR_DPT + 1)];
+            float kk[DR_DPT], qq[DR_DPT];
+#pragma unroll
+            for (int i = 0; i < DR_DPT; i += 4) {
+                *reinterpret_cast<float4*>(&kk[i]) = *reinterpret_cast<const float4*>(&ks[b][tt][part * PS + i]);
+                *reinterpret_cast<float4*>(&qq[i]) = *reinterpret_cast<const float4*>(&qs[b][tt][part * PS + i]);
+            }
             const float beta = sc[b][tt][0], decay = sc[b][tt][1], kq = sc[b][tt][2];
             float sk[4] = {0.f, 0.f, 0.f, 0.f}, sq[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -342,7 +380,7 @@ delta_rule_kernel(const float* __restrict__ prep, const float* __restrict__ bg, 
 using namespace kl;
 
 // proj: compute dtype [rows, ld]; z, x, g at columns z_col, x_col, g_col (width each); out [rows, width].
-// max_new: no sequence brings more rows.  With `chunk_scratch` (float32 [n_seqs * ceil(max_new / 64) * 3 * width]) and a step
+// max_new: no sequence brings more rows.  With `chunk_scratch` (float32 [n_seqs * ceil(max_new / MG_CHUNK) * 3 * width]) and a step
 // long enough to gain from it, the three-pass chunked form runs (3 launches), else one thread walks each channel.
 KL_API int kl_mingru_chunk_tokens() { return MG_CHUNK; }
 
@@ -388,20 +426,28 @@ KL_API int kl_gated_delta_rule(const void* proj, long long ld, int conv_col, int
                                int max_new, int H, int G, int d, int dv, float q_scale, float unit_eps, int dtype,
                                cudaStream_t stream) {
     if (n_seqs <= 0 || max_new <= 0) return KL_OK;
-    if (H <= 0 || G <= 0 || H % G || d <= 0 || dv <= 0 || taps < 1 || d > DR_DPT * 8 || n_seqs > 65535 || G + H > 65535) return KL_ERR_BAD_SIZE;
+    if (H <= 0 || G <= 0 || H % G || d <= 0 || dv <= 0 || taps < 1 || d > 256 || n_seqs > 65535 || G + H > 65535) return KL_ERR_BAD_SIZE;
     const size_t smem = (size_t)(2 * d + 33) * sizeof(float);
-    const int lpc = d <= 32 ? 1 : d <= 64 ? 2 : d <= 128 ? 4 : 8;
+    // 32 key elements per lane; 16 (twice the lanes, half the chain per token) where that still leaves SMs without a CTA
+    int lpc = d <= 32 ? 1 : d <= 64 ? 2 : d <= 128 ? 4 : 8;
+    int dpt = 32;
+    const long long ctas32 = (long long)((dv + DR_THREADS / lpc - 1) / (DR_THREADS / lpc)) * H * n_seqs;
+    if (d > 16 && ctas32 < 2LL * (sm_count() > 0 ? sm_count() : 1)) {
+        dpt = 16;
+        lpc = d <= 32 ? 2 : d <= 64 ? 4 : d <= 128 ? 8 : 16;
+    }
     const dim3 grid1(max_new, n_seqs, G + H);
     const dim3 grid2((dv + DR_THREADS / lpc - 1) / (DR_THREADS / lpc), H, n_seqs);
     if (grid2.y > 65535) return KL_ERR_BAD_SIZE;
-#define KL_DR(T, L) launch_kernel(delta_rule_kernel<T, L>, grid2, DR_THREADS, 0, stream, (const float*)prep, (const float*)bg, (const T*)proj, ld, \
-                                  conv_col, taps, state, state_ld, conv_off, out, cu_tokens, seq_slots, H, G, d, dv)
+#define KL_DR(T, L, D) launch_kernel(delta_rule_kernel<T, L, D>, grid2, DR_THREADS, 0, stream, (const float*)prep, (const float*)bg, (const T*)proj, ld, \
+                                     conv_col, taps, state, state_ld, conv_off, out, cu_tokens, seq_slots, H, G, d, dv)
 #define KL_DELTA(T)                                                                                                          \
     do {                                                                                                                     \
         launch_kernel(delta_prepare_kernel<T>, grid1, DP_THREADS, smem, stream, (const T*)proj, ld, conv_col, b_col, a_col, taps_w, taps, A_log, \
                       dt_bias, (const float*)state, state_ld, conv_off, prep, bg, cu_tokens, seq_slots, H, G, d, dv, q_scale, unit_eps); \
         KL_LAUNCH_CHECK();                                                                                                   \
-        if (lpc == 1) KL_DR(T, 1); else if (lpc == 2) KL_DR(T, 2); else if (lpc == 4) KL_DR(T, 4); else KL_DR(T, 8);          \
+        if (dpt == 32) { if (lpc == 1) KL_DR(T, 1, 32); else if (lpc == 2) KL_DR(T, 2, 32); else if (lpc == 4) KL_DR(T, 4, 32); else KL_DR(T, 8, 32); } \
+        else { if (lpc == 2) KL_DR(T, 2, 16); else if (lpc == 4) KL_DR(T, 4, 16); else if (lpc == 8) KL_DR(T, 8, 16); else KL_DR(T, 16, 16); } \
     } while (0)
     if (dtype == KL_F32) KL_DELTA(float);
     else if (dtype == KL_BF16) KL_DELTA(bf16);
