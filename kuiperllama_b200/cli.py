@@ -28,7 +28,7 @@ def _ids(text: str) -> List[int]:
 
 
 def main(argv: Optional[List[str]] = None) -> int:
-    ap = argparse.ArgumentParser(prog="llama_infer", description="Generate with a Llama 2/3 model folder on a B200.")
+    ap = argparse.ArgumentParser(prog="llama_infer", description="Generate with a model folder (Llama 2/3, Terolix) on a B200.")
     ap.add_argument("checkpoint", nargs="?", default=None, help="model folder with config.json and model.safetensors")
     ap.add_argument("tokenizer", nargs="?", default=None, help="sentencepiece tokenizer.model (optional)")
     ap.add_argument("--prompt", default=None, help='prompt text (needs a tokenizer; the demo\'s default is "hello")')

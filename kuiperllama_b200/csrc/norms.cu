@@ -290,7 +290,10 @@ KL_API int kl_norm_chain(float* residual, const void* delta, long long delta_ld,
                           (T*)out, rows, hidden)
 #define KL_VEC_BY_SIZE(T)                                                                                                    \
             do {                                                                                                             \
-                if (n4 <= 64) KL_VEC(T, 64, 1); else if (n4 <= 128) KL_VEC(T, 128, 1); else if (n4 <= 256) KL_VEC(T, 256, 1);        \
+                /* few rows of a wide model (decode): a row over 1,024 threads, so that one round of loads fetches it */      \
+                if (n_rows <= 256 && n4 > 256 && n4 <= 1024) KL_VEC(T, 1024, 1);                                             \
+                else if (n_rows <= 256 && n4 > 1024) KL_VEC(T, 1024, 2);                                                      \
+                else if (n4 <= 64) KL_VEC(T, 64, 1); else if (n4 <= 128) KL_VEC(T, 128, 1); else if (n4 <= 256) KL_VEC(T, 256, 1);        \
                 else if (n4 <= 512) KL_VEC(T, 256, 2); else if (n4 <= 1024) KL_VEC(T, 256, 4); else KL_VEC(T, 256, 8);             \
             } while (0)
             if (bf) KL_VEC_BY_SIZE(bf16); else KL_VEC_BY_SIZE(float);

@@ -31,7 +31,8 @@ from .csrc import ops
 KERNEL_ENTRY_POINTS = ("embedding", "add_rmsnorm", "swiglu", "rope_kv_write", "attention_simt", "gemm_simt", "argmax_rows",
                        "sample_rows", "token_logprob", "logit_transform", "gemm_tcgen05", "gemm_skinny_stream",
                        "gemm_skinny_partials", "gemm_skinny", "attention_decode", "attention_mma", "attention_tcgen05",
-                       "attention_decode_fused")
+                       "attention_decode_fused", "norm_chain", "head_rmsnorm_gate", "activation", "sigmoid_gate", "mingru_scan",
+                       "gated_delta_rule")
 
 
 class KernelTimes:

@@ -26,13 +26,16 @@ from typing import Dict, List
 import torch
 
 
+SPARE_PAGES = 64       # pages beyond --max-tokens, for the part-filled last page of every live request
+
+
 def main(argv: List[str] = None) -> int:
     ap = argparse.ArgumentParser(prog="trace_run", description=__doc__.split("\n\n")[0])
     ap.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time, each rounded up to a multiple of 64")
+                    help="most tokens live requests hold at any time (padding not counted)")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
 
@@ -42,7 +45,9 @@ def main(argv: List[str] = None) -> int:
     os.makedirs(args.out, exist_ok=True)
     with torch.inference_mode():
         model = load_model(args.model, dtype=args.dtype, device=args.device)
-        max_tokens = max(PAGE, (args.max_tokens + PAGE - 1) // PAGE * PAGE)
+        # --max-tokens counts the tokens themselves, but every live request holds whole pages: up to a page
+        # less one token more for each.  Room for 64 requests' last pages is added (a page is 64 tokens).
+        max_tokens = max(PAGE, (args.max_tokens + PAGE - 1) // PAGE * PAGE) + SPARE_PAGES * PAGE
         cache = model.new_cache(max_tokens=max_tokens)
         engine = Engine(model, cache)
         slots: Dict[str, int] = {}

@@ -361,3 +361,35 @@ def test_cli_runs_a_terolix_folder(folders, capsys):
     for _ in range(4):
         seq.append(int(P.forward_logits(w, c, seq)[-1].argmax()))
     assert " ".join(str(t) for t in seq[3:]) in out
+
+
+def test_trace_run_replays_a_terolix_folder(folders, tmp_path):
+    """bin/trace_run as a user runs it, in float32: five requests of 1, 3, 65, 2 and 66 tokens in one step,
+    then two steps of a token each with the shortest leaving first.  --max-tokens counts tokens, not
+    pages: the five part-filled last pages must fit all the same."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    import numpy as np
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    folder = folders("mixed", seed=1)
+    V = CONFIGS["mixed"]["vocab"]
+    lens = [1, 3, 65, 2, 66]
+    seqs = [tokens(n + 2, V, seed=110 + i) for i, n in enumerate(lens)]
+    steps = [{"step": 0, "entries": [{"id": f"r{i}", "tokens": s[:n], "want": [n - 1]} for i, (s, n) in enumerate(zip(seqs, lens))], "end": []},
+             {"step": 1, "entries": [{"id": f"r{i}", "tokens": [s[n]], "want": [0]} for i, (s, n) in enumerate(zip(seqs, lens))], "end": ["r0"]},
+             {"step": 2, "entries": [{"id": f"r{i}", "tokens": [s[n + 1]], "want": [0]} for i, (s, n) in enumerate(zip(seqs, lens)) if i],
+              "end": [f"r{i}" for i in range(1, 5)]}]
+    out = str(tmp_path / "out")
+    cmd = [sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folder, "--dtype", "float32", "--out", out,
+           "--max-tokens", str(sum(lens) + 2 * len(lens))]
+    p = subprocess.run(cmd, input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-3000:]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+    refs = [oracle_logits(folder, s) for s in seqs]
+    read = lambda k: torch.from_numpy(np.fromfile(os.path.join(out, f"{k}.f32"), dtype="<f4").reshape(-1, V).copy())
+    assert_logits(read(0), torch.stack([r[n - 1] for r, n in zip(refs, lens)]), "float32", "replay: prompts")
+    assert_logits(read(1), torch.stack([r[n] for r, n in zip(refs, lens)]), "float32", "replay: first tokens")
+    assert_logits(read(2), torch.stack([r[n + 1] for r, n in list(zip(refs, lens))[1:]]), "float32", "replay: second tokens")
