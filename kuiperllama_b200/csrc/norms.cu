@@ -294,7 +294,7 @@ KL_API int kl_norm_chain(float* residual, const void* delta, long long delta_ld,
                 if (n_rows <= 256 && n4 > 256 && n4 <= 1024) KL_VEC(T, 1024, 1);                                             \
                 else if (n_rows <= 256 && n4 > 1024) KL_VEC(T, 1024, 2);                                                      \
                 else if (n4 <= 64) KL_VEC(T, 64, 1); else if (n4 <= 128) KL_VEC(T, 128, 1); else if (n4 <= 256) KL_VEC(T, 256, 1);        \
-                else if (n4 <= 512) KL_VEC(T, 256, 2); else if (n4 <= 1024) KL_VEC(T, 256, 4); else KL_VEC(T, 256, 8);             \
+                else if (n4 <= 512) KL_VEC(T, 256, 2); else if (n4 <= 1024) KL_VEC(T, 512, 2); else KL_VEC(T, 512, 4);             \
             } while (0)
             if (bf) KL_VEC_BY_SIZE(bf16); else KL_VEC_BY_SIZE(float);
 #undef KL_VEC_BY_SIZE

@@ -151,7 +151,7 @@ mingru_chunk_kernel(const T* __restrict__ proj, long long ld, int z_col, int x_c
 }
 
 // ------------------------------------------------------------------------------------------ gated delta rule
-// Step 1, one CTA per (token, item): an item is a key head g (the short convolution and SiLU over the
+// Step 1, one CTA per (token or few tokens, item): an item is a key head g (the short convolution and SiLU over the
 // channels of q_g and k_g, unit length for both, q also times q_scale, and k_g . q_g) or a value head h
 // (convolution and SiLU over its dv channels, and the token's beta and decay for that head).  The taps
 // before the step's first token come from the slot's convolution state ([taps - 1][C], C = 2 G d + H dv,
@@ -177,16 +177,18 @@ delta_prepare_kernel(const T* __restrict__ proj, long long ld, int conv_col, int
                      const float* __restrict__ taps_w, int taps, const float* __restrict__ A_log, const float* __restrict__ dt_bias,
                      const float* __restrict__ state, long long state_ld, long long conv_off,
                      float* __restrict__ prep, float* __restrict__ bg, const int* __restrict__ cu_tokens,
-                     const int* __restrict__ seq_slots, int H, int G, int d, int dv, float q_scale, float unit_eps) {
+                     const int* __restrict__ seq_slots, int H, int G, int d, int dv, float q_scale, float unit_eps,
+                     int tokens_per_cta) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float buf[];                        // [2 d] and 33 for the sums
-    const int s = blockIdx.y, j = blockIdx.x, item = blockIdx.z;
+    const int s = blockIdx.y, item = blockIdx.z;
     const int r0 = cu_tokens[s];
-    if (j >= cu_tokens[s + 1] - r0) return;
-    const int row = r0 + j;
+    const int n_new = cu_tokens[s + 1] - r0;
     const int C = 2 * G * d + H * dv;
     const float* cs = state + (size_t)seq_slots[s] * state_ld + conv_off;
+  for (int j = blockIdx.x * tokens_per_cta; j < min((int)(blockIdx.x + 1) * tokens_per_cta, n_new); ++j) {     // a few tokens per CTA in long steps
+    const int row = r0 + j;
     float* o = prep + (size_t)row * C;
     float* b = bg + (size_t)row * (2 * H + G);
     if (item >= G) {
@@ -200,7 +202,7 @@ delta_prepare_kernel(const T* __restrict__ proj, long long ld, int conv_col, int
             b[h] = sigmoidf_(to_f32(pr[b_col + h]));
             b[H + h] = expf(-expf(A_log[h]) * softplusf_(to_f32(pr[a_col + h]) + dt_bias[h]));
         }
-        return;
+        continue;
     }
     const int g = item;
     float* scratch = buf + 2 * d;
@@ -222,6 +224,8 @@ delta_prepare_kernel(const T* __restrict__ proj, long long ld, int conv_col, int
         o[(size_t)(G + g) * d + e] = buf[d + e] * invk;
     }
     if (threadIdx.x == 0) b[2 * H + g] = kq * invq * invk;
+    __syncthreads();                                      // buf is written again for the next token
+  }
 }
 
 // Step 2, the recurrence.  A column j of S (all keys' weights for value element j) never meets
@@ -436,7 +440,8 @@ KL_API int kl_gated_delta_rule(const void* proj, long long ld, int conv_col, int
         dpt = 16;
         lpc = d <= 32 ? 2 : d <= 64 ? 4 : d <= 128 ? 8 : 16;
     }
-    const dim3 grid1(max_new, n_seqs, G + H);
+    const int tpc = max_new >= 256 ? 8 : max_new >= 32 ? 4 : 1;      // tokens a CTA of step 1 walks
+    const dim3 grid1((max_new + tpc - 1) / tpc, n_seqs, G + H);
     const dim3 grid2((dv + DR_THREADS / lpc - 1) / (DR_THREADS / lpc), H, n_seqs);
     if (grid2.y > 65535) return KL_ERR_BAD_SIZE;
 #define KL_DR(T, L, D) launch_kernel(delta_rule_kernel<T, L, D>, grid2, DR_THREADS, 0, stream, (const float*)prep, (const float*)bg, (const T*)proj, ld, \
@@ -444,7 +449,7 @@ KL_API int kl_gated_delta_rule(const void* proj, long long ld, int conv_col, int
 #define KL_DELTA(T)                                                                                                          \
     do {                                                                                                                     \
         launch_kernel(delta_prepare_kernel<T>, grid1, DP_THREADS, smem, stream, (const T*)proj, ld, conv_col, b_col, a_col, taps_w, taps, A_log, \
-                      dt_bias, (const float*)state, state_ld, conv_off, prep, bg, cu_tokens, seq_slots, H, G, d, dv, q_scale, unit_eps); \
+                      dt_bias, (const float*)state, state_ld, conv_off, prep, bg, cu_tokens, seq_slots, H, G, d, dv, q_scale, unit_eps, tpc); \
         KL_LAUNCH_CHECK();                                                                                                   \
         if (dpt == 32) { if (lpc == 1) KL_DR(T, 1, 32); else if (lpc == 2) KL_DR(T, 2, 32); else if (lpc == 4) KL_DR(T, 4, 32); else KL_DR(T, 8, 32); } \
         else { if (lpc == 2) KL_DR(T, 2, 16); else if (lpc == 4) KL_DR(T, 4, 16); else if (lpc == 8) KL_DR(T, 8, 16); else KL_DR(T, 16, 16); } \

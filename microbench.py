@@ -11,6 +11,7 @@ repeats, a buffer larger than L2 written between repeats), and print the achieve
         fixes the number of pieces the decode attention cuts a sequence into, else the package's rule)
     python microbench.py prefill_step --shape 8b --layers 2 --tokens 2048
         (one prompt through a few layers, launched kernel by kernel: the case for a launch list)
+    python microbench.py prefill_step --design terolix --shape 1b --layers 4 --tokens 2048     (the other architecture)
 
 It is also the small case that profiler captures of single kernels are taken on.
 """
@@ -58,16 +59,29 @@ def _paged(n_seqs: int, length: int, kv: int, hd: int):
     return table, k, v
 
 
+def _model_config(args, positions: int) -> dict:
+    """config.json of a few layers of one of bench.py's shapes; with --design terolix the Terolix model that
+    ``bench.py --compare terolix`` sets beside the 1b and 8b shapes."""
+    import bench
+    if args.design == "terolix":
+        z = {"1b": bench.COMPARE_SIZES["1b"], "8b": bench.COMPARE_SIZES["8b-8-layers"]}.get(args.shape)
+        if z is None:
+            raise SystemExit("--design terolix has the shapes 1b and 8b")
+        return bench.terolix_config(z["width"], args.layers, z["heads"], z["kv_heads"], z["head_dim"], z["ff"], 32000)
+    base = {"8b": bench.LLAMA31_8B, "7b": bench.LLAMA2_7B, "1b": bench.LLAMA32_1B, "70b": bench.LLAMA3_70B}[args.shape]
+    return dict(base, num_hidden_layers=args.layers, max_position_embeddings=max(base["max_position_embeddings"], positions))
+
+
 def _decode_step(args) -> int:
     import bench
     import kuiperllama_b200 as kl
     from kuiperllama_b200.config import config_from_dict
     from kuiperllama_b200.engine import Engine, SequenceInput
     from kuiperllama_b200.engine.step import context_class
-    base = {"8b": bench.LLAMA31_8B, "7b": bench.LLAMA2_7B, "1b": bench.LLAMA32_1B, "70b": bench.LLAMA3_70B}[args.shape]
     B, N, L = args.batch, args.context, args.layers
-    cfg = dict(base, num_hidden_layers=L, max_position_embeddings=max(base["max_position_embeddings"], N + args.steps + 16))
+    cfg = _model_config(args, N + args.steps + 16)
     model = kl.random_model(config_from_dict(cfg), seed=0)
+    vocab = model.spec.vocab_size
     rule = ops.decode_attention_splits
     if args.splits:
         ops.decode_attention_splits = lambda n_seqs, kv, hd=128, cls=0: args.splits
@@ -77,7 +91,7 @@ def _decode_step(args) -> int:
     with torch.inference_mode():
         slots = [eng.alloc_slot() for _ in range(B)]
         for s in slots:                                   # one prompt per step keeps the prefill's activations small
-            eng.step([SequenceInput(s, torch.randint(0, cfg["vocab_size"], (N,), generator=g).tolist(), [])])
+            eng.step([SequenceInput(s, torch.randint(0, vocab, (N,), generator=g).tolist(), [])])
         tok = [1] * B
         for _ in range(6):
             eng.decode_step(slots, tok)
@@ -90,8 +104,10 @@ def _decode_step(args) -> int:
         torch.cuda.synchronize()
     eng.check_device_errors()
     us = a.elapsed_time(b) / args.steps * 1e3
-    pieces = args.splits or rule(B, cfg["num_key_value_heads"], cfg["hidden_size"] // cfg["num_attention_heads"], context_class(N + 6))
-    print(json.dumps({"kernel": "decode_step", "shape": args.shape, "layers": L, "batch": B, "context": N, "pieces": pieces,
+    pieces = args.splits
+    if not pieces and args.design == "llama":
+        pieces = rule(B, cfg["num_key_value_heads"], cfg["hidden_size"] // cfg["num_attention_heads"], context_class(N + 6))
+    print(json.dumps({"kernel": "decode_step", "design": args.design, "shape": args.shape, "layers": L, "batch": B, "context": N, "pieces": pieces,
                       "us_per_step": round(us, 1), "us_per_layer": round(us / L, 1)}))
     return 0
 
@@ -101,13 +117,12 @@ def _prefill_step(args) -> int:
     import kuiperllama_b200 as kl
     from kuiperllama_b200.config import config_from_dict
     from kuiperllama_b200.engine import Engine, SequenceInput
-    base = {"8b": bench.LLAMA31_8B, "7b": bench.LLAMA2_7B, "1b": bench.LLAMA32_1B, "70b": bench.LLAMA3_70B}[args.shape]
     T, L = args.tokens, args.layers
-    cfg = dict(base, num_hidden_layers=L, max_position_embeddings=max(base["max_position_embeddings"], T))
+    cfg = _model_config(args, T)
     model = kl.random_model(config_from_dict(cfg), seed=0)
     eng = Engine(model, model.new_cache(max_tokens=T + ops.PAGE, max_seq_len=T), use_graphs=False)
     g = torch.Generator().manual_seed(1)
-    prompt = torch.randint(0, cfg["vocab_size"], (T,), generator=g).tolist()
+    prompt = torch.randint(0, model.spec.vocab_size, (T,), generator=g).tolist()
     times = []
     with torch.inference_mode():
         for _ in range(3 + args.repeats):
@@ -122,7 +137,7 @@ def _prefill_step(args) -> int:
     eng.check_device_errors()
     times = sorted(times[3:])
     ms = times[len(times) // 2]
-    print(json.dumps({"kernel": "prefill_step", "shape": args.shape, "layers": L, "tokens": T, "ms": round(ms, 3),
+    print(json.dumps({"kernel": "prefill_step", "design": args.design, "shape": args.shape, "layers": L, "tokens": T, "ms": round(ms, 3),
                       "us_per_layer": round(ms * 1e3 / L, 1)}))
     return 0
 
@@ -132,6 +147,9 @@ def main(argv=None) -> int:
     ap.add_argument("kernel", choices=["gemm_skinny", "gemm_tcgen05", "attention_prefill", "attention_decode", "decode_step",
                                            "prefill_step"])
     ap.add_argument("--shape", default="8b", choices=["8b", "7b", "1b", "70b"], help="decode_step: which of bench.py's shapes")
+    ap.add_argument("--design", default="llama", choices=["llama", "terolix"],
+                    help="decode_step, prefill_step: the Llama shape, or the Terolix model of that width (1b, 8b; layers in the order "
+                         "minGRU, minGRU, attention, delta rule)")
     ap.add_argument("--layers", type=int, default=4, help="decode_step: layers of the model")
     ap.add_argument("--steps", type=int, default=150, help="decode_step: timed steps")
     ap.add_argument("--m", type=int, default=8)
