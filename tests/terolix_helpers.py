@@ -46,6 +46,10 @@ CONFIGS: Dict[str, dict] = {
         {"type": "delta", "mixer": {"heads": 4, "kv_heads": 2, "dim": 128, "vdim": 128, "conv": 2}, "mlp": _ff(192)},
         {"type": "mingru", "mixer": {"width": 384}, "mlp": _ff(128)}]},
 }
+# query heads in groups larger than the tensor-core decode kernel's 16: 24 on one key head, head sizes 64 and 32
+CONFIGS["grouped"] = {"architecture": "Terolix", "vocab": 83, "width": 96, "norm": {"eps": 1e-5}, "layers": [
+    {"type": "attention", "mixer": {"heads": 24, "kv_heads": 1, "dim": 64, "vdim": 64, "scale": 0.15, "rot": _rot(32, 20000.0)}, "mlp": _ff(64)},
+    {"type": "attention", "mixer": {"heads": 24, "kv_heads": 1, "dim": 32, "vdim": 32, "scale": 0.2, "rot": _rot(8)}, "mlp": None}]}
 # one layer of each mechanism alone (the attention of "needle" is built by the test that uses it)
 for _kind, _layer in (("mingru", CONFIGS["mixed"]["layers"][0]), ("attention", CONFIGS["mixed"]["layers"][1]),
                       ("delta", CONFIGS["mixed"]["layers"][2])):

@@ -168,7 +168,7 @@ def test_kernels_against_the_plain_functions(dtype):
 # ----------------------------------------------------------------------------- whole models, cut in every way
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", FULL)
+@pytest.mark.parametrize("name", FULL + ["grouped"])
 def test_whole_prompt_and_token_by_token(models, name, dtype):
     """150 tokens at once (keys in three pages), and the same one by one from the first token on."""
     model, folder = models(name, dtype, seed=1)
