@@ -93,6 +93,8 @@ class PagedGroup:
     ``window`` in the request, pages that no query can reach any more go back to the pool while
     the sequence grows."""
 
+    stores_values = True          # False: one tensor per execution; ``v`` is ``k`` (values are columns of the keys' rows)
+
     def __init__(self, request: KVRequest, entries: List[int], n_pages: int, n_slots: int, blocks_per_seq: int,
                  dtype: torch.dtype, device: torch.device, window_step_tokens: Optional[int] = None):
         self.request = request
@@ -105,7 +107,7 @@ class PagedGroup:
         self.blocks_per_seq = blocks_per_seq
         shape = (len(entries), n_pages, request.kv_heads, PAGE, request.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        self.v = torch.zeros(shape, dtype=dtype, device=device) if self.stores_values else self.k
         # Pageable on purpose: a copy from pageable memory is staged before the call returns,
         # so the host may rewrite a row (a slot that is reused) while an earlier step's copy
         # is still queued on the device.
@@ -161,7 +163,16 @@ class PagedGroup:
         return self.pages.n
 
     def bytes(self) -> int:
-        return self.k.numel() * self.k.element_size() * 2
+        return self.k.numel() * self.k.element_size() * (2 if self.stores_values else 1)
+
+
+@register_cache_kind("keys")
+class KeysOnlyGroup(PagedGroup):
+    """Paged rows without a second tensor for values: a mixer whose values are columns of its keys' rows
+    (attention over a shared latent: one row [latent | rotated key part] per token, ``kv_heads`` = 1) asks
+    for this kind; its view's ``v`` is the key tensor itself."""
+
+    stores_values = False
 
 
 class SequenceCache:

@@ -4,7 +4,8 @@ from .registry import (ConfigError, config_class, config_from_dict, config_from_
 from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, default_schedule
 from .llama import Llama3RopeScaling, LlamaConfig
 from .terolix import TerolixConfig
+from .munadra import MunadraConfig
 
 __all__ = ["ConfigError", "config_class", "config_from_dict", "config_from_file", "config_from_folder",
            "known_architectures", "register_architecture", "LayerSpec", "ModelSpec", "PartSpec",
-           "ScheduleEntry", "default_schedule", "Llama3RopeScaling", "LlamaConfig", "TerolixConfig"]
+           "ScheduleEntry", "default_schedule", "Llama3RopeScaling", "LlamaConfig", "TerolixConfig", "MunadraConfig"]

@@ -2,7 +2,7 @@
 //
 // This is the kernel of the true 32-bit path (prefill and decode) and the fallback of the
 // bfloat16 path for sizes and options that the tensor-core kernels refuse (a window, a
-// head size that is not on their list; any head size up to 256 runs here).  One CTA of four warps per
+// head size that is not on their list; any key size and value sizes up to 512 run here).  One CTA of four warps per
 // (token, query head).  Query token t of slot s at position p reads keys lo..p of that
 // slot, lo = max(0, p - window + 1) with a window, else 0.  Head h reads kv head
 // h / (H / KV); score = (q . k) * scale; softmax with the maximum subtracted; o = sum p v
@@ -12,12 +12,17 @@
 // Keys are cut into chunks of 32 by absolute position and the chunks are dealt to the warps
 // round-robin, so the order of every sum depends only on the token's own position: the
 // result does not change with the way tokens are cut into steps or batched.
+//
+// Options beyond KuiperLLama's attention: values of another size than the keys (`vd` columns of rows
+// that are `v_ld` apart; with v_cache == k_cache and v_ld == hd the values are the leading columns of
+// the keys, which is what attention over a shared latent reads), and a sink: a learned number per
+// head that joins the softmax's denominator as exp(sink) and has no value.
 #include "common.cuh"
 
 namespace kl {
 
 constexpr int ATT_WARPS = 4;
-constexpr int ATT_MAX_PER_LANE = 8;      // head_dim <= 256
+constexpr int ATT_MAX_VALUE_DIM = 512;   // value columns per head (32 lanes x PL, PL = 8 or 16)
 
 template <typename T>
 __device__ __forceinline__ float dot_row(const T* __restrict__ k, const float* __restrict__ q, int hd);
@@ -56,20 +61,20 @@ __device__ __forceinline__ float dot_row<bf16>(const bf16* __restrict__ k, const
     return s;
 }
 
-template <typename T>
+template <typename T, int PL>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out,
                       const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                       const int* __restrict__ block_table, int blocks_per_seq,
                       const int* __restrict__ positions, const int* __restrict__ token_slot,
-                      int H, int KV, int hd, float scale, int window) {
+                      int H, int KV, int hd, float scale, int window, int vd, int v_ld, const float* __restrict__ sink) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float smem[];
     float* q_s = smem;                               // [hd]
     float* m_s = q_s + hd;                           // [ATT_WARPS]
     float* l_s = m_s + ATT_WARPS;                    // [ATT_WARPS]
-    float* acc_s = l_s + ATT_WARPS;                  // [ATT_WARPS][hd]
+    float* acc_s = l_s + ATT_WARPS;                  // [ATT_WARPS][vd]
 
     const int t = blockIdx.x, h = blockIdx.y;
     const int slot = token_slot[t];
@@ -84,9 +89,9 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
 
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     float m = -INFINITY, l = 0.f;
-    float acc[ATT_MAX_PER_LANE];
+    float acc[PL];
 #pragma unroll
-    for (int i = 0; i < ATT_MAX_PER_LANE; ++i) acc[i] = 0.f;
+    for (int i = 0; i < PL; ++i) acc[i] = 0.f;
 
     const int* table = block_table + (size_t)slot * blocks_per_seq;
     for (int c = lo / 32 + warp; c * 32 <= pos; c += ATT_WARPS) {
@@ -103,41 +108,43 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
         l = l * corr + warp_sum(p);
         m = m_new;
 #pragma unroll
-        for (int i = 0; i < ATT_MAX_PER_LANE; ++i) acc[i] *= corr;
+        for (int i = 0; i < PL; ++i) acc[i] *= corr;
         const int j_lo = max(lo - base, 0), j_hi = min(pos - base, 31);
-        const T* vbase = v_cache + page_off;
+        const T* vbase = v_cache + (((size_t)page * KV + g) * PAGE + (base % PAGE)) * (size_t)v_ld;
         for (int j = j_lo; j <= j_hi; ++j) {
             const float pj = __shfl_sync(0xffffffffu, p, j);
-            const T* vrow = vbase + (size_t)j * hd;
+            const T* vrow = vbase + (size_t)j * v_ld;
 #pragma unroll
-            for (int i = 0; i < ATT_MAX_PER_LANE; ++i) {
+            for (int i = 0; i < PL; ++i) {
                 const int d = lane + 32 * i;
-                if (d < hd) acc[i] += pj * to_f32(vrow[d]);
+                if (d < vd) acc[i] += pj * to_f32(vrow[d]);
             }
         }
     }
     if (lane == 0) { m_s[warp] = m; l_s[warp] = l; }
 #pragma unroll
-    for (int i = 0; i < ATT_MAX_PER_LANE; ++i) {
+    for (int i = 0; i < PL; ++i) {
         const int d = lane + 32 * i;
-        if (d < hd) acc_s[warp * hd + d] = acc[i];
+        if (d < vd) acc_s[warp * vd + d] = acc[i];
     }
     __syncthreads();
     float M = m_s[0];
 #pragma unroll
     for (int w = 1; w < ATT_WARPS; ++w) M = fmaxf(M, m_s[w]);
-    float L = 0.f;
+    const float snk = sink ? sink[h] : -INFINITY;
+    M = fmaxf(M, snk);
+    float L = sink ? expf(snk - M) : 0.f;
     float wgt[ATT_WARPS];
 #pragma unroll
     for (int w = 0; w < ATT_WARPS; ++w) {
         wgt[w] = m_s[w] == -INFINITY ? 0.f : expf(m_s[w] - M);
         L += l_s[w] * wgt[w];
     }
-    T* orow = out + ((size_t)t * H + h) * hd;
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    T* orow = out + ((size_t)t * H + h) * vd;
+    for (int d = threadIdx.x; d < vd; d += blockDim.x) {
         float o = 0.f;
 #pragma unroll
-        for (int w = 0; w < ATT_WARPS; ++w) o += acc_s[w * hd + d] * wgt[w];
+        for (int w = 0; w < ATT_WARPS; ++w) o += acc_s[w * vd + d] * wgt[w];
         orow[d] = from_f32<T>(o / L);
     }
 }
@@ -146,26 +153,30 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
 
 using namespace kl;
 
-// q: rows of q_stride elements, head h at column h * hd.  out: [tokens, H * hd].
+// q: rows of q_stride elements, head h at column h * hd.  out: [tokens, H * vd].  vd <= 0 means values like
+// keys (vd = v_ld = hd).  sink: float32 [H] or null.
 KL_API int kl_attention_simt(const void* q, int q_stride, void* out, const void* k_cache, const void* v_cache,
                              const int* block_table, int blocks_per_seq, const int* positions,
                              const int* token_slot, int n_tokens, int H, int KV, int hd, float scale, int window,
-                             int dtype, cudaStream_t stream) {
+                             int vd, int v_ld, const float* sink, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return KL_OK;
-    if (hd > 32 * ATT_MAX_PER_LANE || hd <= 0 || KV <= 0 || H % KV) return KL_ERR_BAD_SIZE;
+    if (vd <= 0) { vd = hd; v_ld = hd; }
+    if (vd > ATT_MAX_VALUE_DIM || hd <= 0 || v_ld < vd || KV <= 0 || H % KV) return KL_ERR_BAD_SIZE;
     if (H > 65535) return KL_ERR_BAD_SIZE;
     const dim3 grid(n_tokens, H);
-    const size_t smem = (size_t)(hd + 2 * ATT_WARPS + ATT_WARPS * hd) * sizeof(float);
-    if (dtype == KL_F32)
-        launch_kernel(attention_simt_kernel<float>, grid, ATT_WARPS * 32, smem, stream, (const float*)q, q_stride, (float*)out,
-            (const float*)k_cache, (const float*)v_cache, block_table, blocks_per_seq, positions, token_slot, H, KV,
-            hd, scale, window);
-    else if (dtype == KL_BF16)
-        launch_kernel(attention_simt_kernel<bf16>, grid, ATT_WARPS * 32, smem, stream, (const bf16*)q, q_stride, (bf16*)out,
-            (const bf16*)k_cache, (const bf16*)v_cache, block_table, blocks_per_seq, positions, token_slot, H, KV,
-            hd, scale, window);
-    else
-        return KL_ERR_BAD_DTYPE;
+    const size_t smem = (size_t)(hd + 2 * ATT_WARPS + ATT_WARPS * vd) * sizeof(float);
+    if (smem > 200 * 1024) return KL_ERR_BAD_SIZE;
+#define KL_ATT(T, PL)                                                                                                         \
+    do {                                                                                                                      \
+        if (smem > 48 * 1024) KL_CUDA(cudaFuncSetAttribute(attention_simt_kernel<T, PL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        launch_kernel(attention_simt_kernel<T, PL>, grid, ATT_WARPS * 32, smem, stream, (const T*)q, q_stride, (T*)out,       \
+                      (const T*)k_cache, (const T*)v_cache, block_table, blocks_per_seq, positions, token_slot, H, KV, hd,    \
+                      scale, window, vd, v_ld, sink);                                                                         \
+    } while (0)
+    if (dtype == KL_F32) { if (vd <= 256) KL_ATT(float, 8); else KL_ATT(float, 16); }
+    else if (dtype == KL_BF16) { if (vd <= 256) KL_ATT(bf16, 8); else KL_ATT(bf16, 16); }
+    else return KL_ERR_BAD_DTYPE;
+#undef KL_ATT
     KL_LAUNCH_CHECK();
     return KL_OK;
 }

@@ -37,6 +37,10 @@ SOURCES: Dict[str, str] = {
     "gemm_simt": "gemm_simt.cu",
     "gemm_tcgen05": "gemm_tcgen05.cu",
     "sampling": "sampling.cu",
+    "grouped_gemm": "grouped_gemm.cu",
+    "moe": "moe.cu",
+    "latent": "latent.cu",
+    "linear_recurrence": "linear_recurrence.cu",
 }
 HEADERS: List[str] = ["common.cuh", "tcgen05.cuh", "tma_host.cuh", "attention_decode_noalloc.h"]
 

@@ -54,16 +54,18 @@ __global__ void activation_vec_kernel(const T* __restrict__ x, long long ld_x, T
     }
 }
 
-// x[t, i] *= sigmoid(gate[t, i]) in place.
+// x[t, i] *= sigmoid(gate[t, i / group]) in place: group = 1 gates element by element, group = a head's
+// width gates every head by one number.
 template <typename T>
-__global__ void sigmoid_gate_kernel(T* __restrict__ x, long long ld_x, const T* __restrict__ gate, long long ld_gate, int tokens, int n) {
+__global__ void sigmoid_gate_kernel(T* __restrict__ x, long long ld_x, const T* __restrict__ gate, long long ld_gate, int tokens, int n,
+                                    int group) {
     pdl_launch_dependents();
     pdl_wait();
     const size_t total = (size_t)tokens * n;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / n;
         const int i = (int)(idx - t * n);
-        const float g = to_f32(gate[t * ld_gate + i]);
+        const float g = to_f32(gate[t * ld_gate + i / group]);
         x[t * ld_x + i] = from_f32<T>(to_f32(x[t * ld_x + i]) * (1.0f / (1.0f + expf(-g))));
     }
 }
@@ -97,15 +99,16 @@ KL_API int kl_activation(const void* x, long long ld_x, void* out, long long ld_
     return KL_OK;
 }
 
-KL_API int kl_sigmoid_gate(void* x, long long ld_x, const void* gate, long long ld_gate, int tokens, int n, int dtype,
+KL_API int kl_sigmoid_gate(void* x, long long ld_x, const void* gate, long long ld_gate, int tokens, int n, int group, int dtype,
                            cudaStream_t stream) {
     if (tokens <= 0 || n <= 0) return KL_OK;
+    if (group <= 0 || n % group) return KL_ERR_BAD_SIZE;
     const int threads = 256;
     const int blocks = kl::strided_grid((size_t)tokens * n, threads, 16);
     if (dtype == KL_F32)
-        launch_kernel(sigmoid_gate_kernel<float>, blocks, threads, 0, stream, (float*)x, ld_x, (const float*)gate, ld_gate, tokens, n);
+        launch_kernel(sigmoid_gate_kernel<float>, blocks, threads, 0, stream, (float*)x, ld_x, (const float*)gate, ld_gate, tokens, n, group);
     else if (dtype == KL_BF16)
-        launch_kernel(sigmoid_gate_kernel<bf16>, blocks, threads, 0, stream, (bf16*)x, ld_x, (const bf16*)gate, ld_gate, tokens, n);
+        launch_kernel(sigmoid_gate_kernel<bf16>, blocks, threads, 0, stream, (bf16*)x, ld_x, (const bf16*)gate, ld_gate, tokens, n, group);
     else
         return KL_ERR_BAD_DTYPE;
     KL_LAUNCH_CHECK();

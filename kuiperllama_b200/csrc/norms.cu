@@ -6,7 +6,8 @@
 //     d = d * sigmoid(gate[s] + gate_bias)          (a gated residual, if a gate is given)
 //     d = norm_post(d)                              (a norm after the sublayer, if one is given)
 //     x = residual[s] + d;  residual[s] = x         (32-bit sum, written back)
-//     out[r] = norm(x)                              (the norm before the next sublayer, if out is given)
+//     out[r] = norm(x)                              (the norm before the next sublayer, if out is given; it may be
+//                                                    "none": the row itself in the compute dtype)
 //
 // so that a block whose sublayers are normed before and after costs one row-wise kernel per
 // sublayer, as the pre-norm block's add_rmsnorm does.  Each norm is a layer norm
@@ -21,11 +22,12 @@
 
 namespace kl {
 
-enum : int { NORM_LAYER = 0, NORM_RMS = 1 };
+enum : int { NORM_LAYER = 0, NORM_RMS = 1, NORM_NONE = 2 };     // NORM_NONE: the rows as they are (no weight is read)
 
 // Normalise buf[0..n) in place (shared memory, every thread strides over it).
 __device__ __forceinline__ void norm_in_place(float* buf, int n, const float* __restrict__ w, const float* __restrict__ b,
                                               float eps, int kind, float* scratch) {
+    if (kind == NORM_NONE) return;
     float mean = 0.f;
     if (kind == NORM_LAYER) {
         float s = 0.f;
@@ -80,6 +82,7 @@ __device__ __forceinline__ float block_sum_once(float v, float* scratch) {
 template <int THREADS, int VPT>
 __device__ __forceinline__ void norm_in_registers(float4 (&v)[VPT], int n4, int n, const float* __restrict__ w,
                                                   const float* __restrict__ b, float eps, int kind, float* scratch) {
+    if (kind == NORM_NONE) return;
     float mean = 0.f;
     if (kind == NORM_LAYER) {
         float s = 0.f;
@@ -272,7 +275,8 @@ KL_API int kl_norm_chain(float* residual, const void* delta, long long delta_ld,
                          const float* w, const float* b, float eps, int kind, void* out, const int* rows, int n_rows,
                          int hidden, int dtype, cudaStream_t stream) {
     if (n_rows <= 0) return KL_OK;
-    if (hidden <= 0 || (out != nullptr && w == nullptr)) return KL_ERR_BAD_SIZE;
+    if (hidden <= 0 || (out != nullptr && w == nullptr && kind != NORM_NONE)) return KL_ERR_BAD_SIZE;
+    if (kind < NORM_LAYER || kind > NORM_NONE || post_kind < NORM_LAYER || post_kind > NORM_NONE) return KL_ERR_BAD_SIZE;
     if (n_partials < 0 || (n_partials > 0 && (partials == nullptr || delta != nullptr))) return KL_ERR_BAD_SIZE;
     const bool bf = dtype == KL_BF16;
     if (dtype != KL_F32 && !bf) return KL_ERR_BAD_DTYPE;
@@ -303,7 +307,6 @@ KL_API int kl_norm_chain(float* residual, const void* delta, long long delta_ld,
             return KL_OK;
         }
     }
-    if ((kind != NORM_LAYER && kind != NORM_RMS) || (post_kind != NORM_LAYER && post_kind != NORM_RMS)) return KL_ERR_BAD_SIZE;
     const size_t smem = (size_t)(hidden + 33) * sizeof(float);
     if (smem > 200 * 1024) return KL_ERR_BAD_SIZE;
     const int threads = hidden >= 1024 ? 256 : 128;

@@ -172,7 +172,7 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
 
 # --------------------------------------------------------------------------- norm chains, activations, gates
 
-NORM_KINDS = {"layernorm": 0, "rmsnorm": 1}
+NORM_KINDS = {"layernorm": 0, "rmsnorm": 1, "none": 2}      # "none": the rows themselves in the compute dtype
 ACTIVATIONS = {"xielu": 0, "gelu_tanh": 1, "silu": 2}
 
 
@@ -211,8 +211,8 @@ def norm_chain(residual: torch.Tensor, delta: Optional[torch.Tensor], out: Optio
     for t in (weight, bias, gate_bias) + (tuple(post[:2]) if post is not None else ()):
         _need(t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == hidden), "norm_chain: float32 [hidden] vectors")
     if out is not None:
-        _need(out.is_contiguous() and out.dtype == dtype and out.shape[-1] == hidden and out.shape[0] >= n and weight is not None,
-              "norm_chain: output shape")
+        _need(out.is_contiguous() and out.dtype == dtype and out.shape[-1] == hidden and out.shape[0] >= n
+              and (weight is not None or kind == "none"), "norm_chain: output shape")
     pw, pb, peps, pkind = post if post is not None else (None, None, 0.0, kind)
     _check(lib("norms").kl_norm_chain(
         _ptr(residual), _ptr(delta), ctypes.c_longlong(delta.stride(0) if delta is not None else 0), _ptr(parts), n_parts,
@@ -250,14 +250,16 @@ def activation(x: torch.Tensor, out: torch.Tensor, kind: str, params: Optional[t
                                             ACTIVATIONS[kind], _ptr(params), dtype_code(x.dtype), _stream()), "activation")
 
 
-def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor) -> None:
-    """x *= sigmoid(gate) in place; both [tokens, width] in the compute dtype, any row stride."""
+def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor, group: int = 1) -> None:
+    """x[t, i] *= sigmoid(gate[t, i // group]) in place; x [tokens, width] and gate [tokens, width / group] in the
+    compute dtype, any row stride.  ``group`` = a head's width gates every head by one number."""
     _cuda(x, gate)
     n, width = x.shape
-    _columns(x, n, width, "sigmoid_gate: x"); _columns(gate, n, width, "sigmoid_gate: gate")
+    _need(group >= 1 and width % group == 0, "sigmoid_gate: the width must be a multiple of the group")
+    _columns(x, n, width, "sigmoid_gate: x"); _columns(gate, n, width // group, "sigmoid_gate: gate")
     _need(x.dtype == gate.dtype, "sigmoid_gate: dtypes differ")
     _check(lib("elementwise").kl_sigmoid_gate(_ptr(x), ctypes.c_longlong(x.stride(0)), _ptr(gate), ctypes.c_longlong(gate.stride(0)),
-                                              n, width, dtype_code(x.dtype), _stream()), "sigmoid_gate")
+                                              n, width, group, dtype_code(x.dtype), _stream()), "sigmoid_gate")
 
 
 # --------------------------------------------------------------------------- recurrent mixers
@@ -362,21 +364,199 @@ def rope_kv_write(qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], rotary_di
 
 def attention_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                    block_table: torch.Tensor, positions: torch.Tensor, token_slot: torch.Tensor, n_tokens: int,
-                   num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: int = 0) -> None:
-    """out[t, h] = softmax(scale * q[t, h] . K[slot_t, lo..pos_t]) V over the paged cache."""
-    _cuda(q, out, k_cache, v_cache, block_table, positions, token_slot)
+                   num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: int = 0,
+                   value_dim: Optional[int] = None, sink: Optional[torch.Tensor] = None) -> None:
+    """out[t, h] = softmax(scale * q[t, h] . K[slot_t, lo..pos_t]) V over the paged cache.  ``value_dim``: the
+    values are the first so many columns of ``v_cache``'s rows (which may be the key cache itself);
+    ``sink``: float32 [heads], exp(sink[h]) joins head h's denominator."""
+    _cuda(q, out, k_cache, v_cache, block_table, positions, token_slot, sink)
     _i32(positions, "positions"); _i32(token_slot, "token_slot"); _i32(block_table, "block_table")
-    _need(out.is_contiguous() and out.shape[0] >= n_tokens and out.shape[1] == num_heads * head_dim, "attention: out shape")
+    vd = head_dim if value_dim is None else int(value_dim)
+    _need(out.is_contiguous() and out.shape[0] >= n_tokens and out.shape[1] == num_heads * vd, "attention: out shape")
     _need(q.dtype == out.dtype == k_cache.dtype == v_cache.dtype, "attention: dtypes differ")
     _need(k_cache.is_contiguous() and v_cache.is_contiguous()
           and tuple(k_cache.shape[1:]) == (num_kv_heads, PAGE, head_dim), "attention: cache layout")
-    _need(0 < head_dim <= 256, f"attention: head_dim {head_dim} must be at most 256")
+    _need(tuple(v_cache.shape[1:3]) == (num_kv_heads, PAGE) and v_cache.shape[3] >= vd, "attention: value cache layout")
+    _need(0 < vd <= 512, f"attention: value size {vd} must be at most 512")
     _need(num_heads % num_kv_heads == 0, "attention: heads must be a multiple of kv heads")
+    _need(sink is None or (sink.dtype == torch.float32 and sink.is_contiguous() and sink.numel() == num_heads), "attention: sink")
     _check(lib("attention_simt").kl_attention_simt(_ptr(q), q_stride, _ptr(out), _ptr(k_cache), _ptr(v_cache),
                                                    _ptr(block_table), block_table.shape[1], _ptr(positions),
                                                    _ptr(token_slot), n_tokens, num_heads, num_kv_heads, head_dim,
-                                                   ctypes.c_float(scale), int(window or 0), dtype_code(q.dtype),
-                                                   _stream()), "attention_simt")
+                                                   ctypes.c_float(scale), int(window or 0), vd, int(v_cache.shape[3]), _ptr(sink),
+                                                   dtype_code(q.dtype), _stream()), "attention_simt")
+
+
+# --------------------------------------------------------------------------- grouped products
+
+def grouped_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, a_group_stride: int = 0, out_group_stride: int = 0,
+                 rows: Optional[int] = None, a_rows: Optional[torch.Tensor] = None, tile_group: Optional[torch.Tensor] = None,
+                 tile_rows: int = 64, gated: Optional[tuple] = None) -> None:
+    """out_g = a_g @ w[g]^T for every group g, with ``w`` [groups, N (2 N if gated), K].
+
+    Batched (``tile_group`` None): all ``rows`` rows for every group; group g reads the columns of ``a`` from
+    g * a_group_stride and writes the columns of ``out`` from g * out_group_stride.  Routed: ``tile_group``
+    [tiles] names the group of every tile of ``tile_rows`` list places (-1: none) and ``a_rows`` [tiles *
+    tile_rows] the row of ``a`` each place reads (-1: padding; None: the place itself); ``out`` is indexed by
+    place.  ``gated`` = (limit, alpha, shift): the weights hold N gate rows then N up rows and the result
+    is min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u, -limit, limit) + shift); limit <= 0 clamps nothing."""
+    _cuda(a, w, out, a_rows, tile_group)
+    _i32(a_rows, "a_rows"); _i32(tile_group, "tile_group")
+    _need(w.dim() == 3 and w.is_contiguous() and a.dtype == w.dtype, "grouped_gemm: weights must be contiguous [groups, N, K] in a's dtype")
+    G, NW, K = w.shape
+    N = NW // 2 if gated is not None else NW
+    _need(gated is None or NW % 2 == 0, "grouped_gemm: gated weights hold gate rows and up rows")
+    _need(a.dim() == 2 and a.stride(1) == 1 and out.dim() == 2 and out.stride(1) == 1, "grouped_gemm: rows must be contiguous")
+    _need(tile_rows in (16, 64), "grouped_gemm: tiles of 16 or 64 rows")
+    if tile_group is None:
+        M = a.shape[0] if rows is None else int(rows)
+        _need(a_rows is None and M <= a.shape[0] and M <= out.shape[0], "grouped_gemm: rows")
+        _need((G - 1) * a_group_stride + K <= a.shape[1] and (G - 1) * out_group_stride + N <= out.shape[1], "grouped_gemm: columns")
+        tiles = 0
+    else:
+        tiles = tile_group.numel()
+        M = tiles * tile_rows
+        _need(out.shape[0] >= M and out.shape[1] >= N and a.shape[1] >= K, "grouped_gemm: shapes")
+        _need(a_rows is None or a_rows.numel() >= M, "grouped_gemm: one source row per list place")
+        _need(a_rows is not None or a.shape[0] >= M, "grouped_gemm: a holds fewer rows than the list")
+        a_group_stride = out_group_stride = 0
+    lim, alpha, shift = gated if gated is not None else (0.0, 1.0, 0.0)
+    _check(lib("grouped_gemm").kl_grouped_gemm(
+        _ptr(a), ctypes.c_longlong(a.stride(0)), ctypes.c_longlong(a_group_stride), _ptr(a_rows), _ptr(w), ctypes.c_longlong(NW * K),
+        _ptr(out), ctypes.c_longlong(out.stride(0)), ctypes.c_longlong(out_group_stride), _ptr(tile_group), tiles, tile_rows, G, M, N, K,
+        int(gated is not None), ctypes.c_float(lim), ctypes.c_float(alpha), ctypes.c_float(shift), dtype_code(a.dtype),
+        dtype_code(out.dtype), _stream()), "grouped_gemm")
+
+
+# --------------------------------------------------------------------------- mixture of experts
+
+MOE_MAX_EXPERTS = 256          # equals MOE_MAX_EXPERTS in moe.cu
+
+
+def moe_route(logits: torch.Tensor, top: int, renormalise: bool = False):
+    """(choice int32 [tokens, top], weight float32 [tokens, top]) from float32 router logits [tokens, experts]:
+    softmax over all experts, the ``top`` largest, their scores (divided by their sum if ``renormalise``)."""
+    _cuda(logits)
+    n, E = logits.shape
+    _need(logits.dtype == torch.float32 and logits.stride(1) == 1, "moe_route: float32 logits")
+    _need(0 < top <= E <= MOE_MAX_EXPERTS, f"moe_route: {top} of {E} experts (at most {MOE_MAX_EXPERTS})")
+    choice = torch.empty((n, top), dtype=torch.int32, device=logits.device)
+    weight = torch.empty((n, top), dtype=torch.float32, device=logits.device)
+    _check(lib("moe").kl_moe_route(_ptr(logits), ctypes.c_longlong(logits.stride(0)), n, E, top, int(bool(renormalise)), _ptr(choice),
+                                   _ptr(weight), _stream()), "moe_route")
+    return choice, weight
+
+
+def moe_plan(choice: torch.Tensor, experts: int, tile_rows: int, token_slot: Optional[torch.Tensor] = None):
+    """The list of (token, choice) pairs sorted by expert, every expert's run padded to whole tiles:
+    (pair_pos int32 [tokens * top]: each pair's place, -1 for rows that belong to no sequence; list_rows int32
+    [cap]: the token row of every place, -1 for padding; tile_group int32 [cap / tile_rows]: the expert of every tile)."""
+    _cuda(choice, token_slot)
+    _i32(choice, "choice"); _i32(token_slot, "token_slot")
+    n, top = choice.shape
+    cap = -(-(n * top + experts * (tile_rows - 1)) // tile_rows) * tile_rows
+    tiles = cap // tile_rows
+    dev = choice.device
+    scratch = torch.empty(2 * n * top + cap + tiles, dtype=torch.int32, device=dev)
+    rank, pair_pos, list_rows, tile_group = torch.split(scratch, [n * top, n * top, cap, tiles])
+    _need(token_slot is None or token_slot.numel() >= n, "moe_plan: one slot per row")
+    _check(lib("moe").kl_moe_plan(_ptr(choice), _ptr(token_slot), n, top, experts, tile_rows, cap, tiles, _ptr(rank), _ptr(pair_pos),
+                                  _ptr(list_rows), _ptr(tile_group), _stream()), "moe_plan")
+    return pair_pos, list_rows, tile_group
+
+
+def moe_combine(results: torch.Tensor, pair_pos: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = sum_k weight[t, k] * results[pair_pos[t * top + k]] (float32 [tokens, hidden]), in the order of k."""
+    _cuda(results, pair_pos, weight, out)
+    n, top = weight.shape
+    _need(out.dtype == torch.float32 and out.is_contiguous() and out.shape[0] >= n and results.stride(1) == 1
+          and results.shape[1] == out.shape[1], "moe_combine: shapes")
+    _check(lib("moe").kl_moe_combine(_ptr(results), ctypes.c_longlong(results.stride(0)), _ptr(pair_pos), _ptr(weight), n, top,
+                                     out.shape[1], _ptr(out), dtype_code(results.dtype), _stream()), "moe_combine")
+
+
+# --------------------------------------------------------------------------- attention over a shared latent
+
+def latent_prepare(proj: torch.Tensor, q_col: int, kv_col: Optional[int], norm_weight: Optional[torch.Tensor], eps: float,
+                   inv_freq: Optional[torch.Tensor], rot_dims: int, mscale: float, interleaved: bool, positions: torch.Tensor,
+                   token_slot: torch.Tensor, block_table: Optional[torch.Tensor], cache: Optional[torch.Tensor], qfull: torch.Tensor,
+                   n_tokens: int, heads: int, dim: int, rot_dim: int, kv_rank: int) -> None:
+    """Per token: the normed latent and the rotated shared key part into the cache row (unless ``kv_col`` is
+    None: the layer reads another layer's cache), and every head's rotated query part into the last
+    ``rot_dim`` columns of its [kv_rank + rot_dim] slice of ``qfull`` (see latent.cu)."""
+    _cuda(proj, norm_weight, inv_freq, positions, token_slot, block_table, cache, qfull)
+    _i32(positions, "positions"); _i32(token_slot, "token_slot"); _i32(block_table, "block_table")
+    Dk = kv_rank + rot_dim
+    _need(proj.dim() == 2 and proj.stride(1) == 1 and q_col + heads * (dim + rot_dim) <= proj.shape[1], "latent_prepare: projections")
+    _need(qfull.is_contiguous() and qfull.dtype == proj.dtype and qfull.shape[0] >= n_tokens and qfull.shape[1] == heads * Dk,
+          "latent_prepare: query buffer")
+    if kv_col is not None:
+        _need(kv_col + Dk <= proj.shape[1], "latent_prepare: the down-projection's columns")
+        _need(cache is not None and cache.is_contiguous() and cache.dtype == proj.dtype and tuple(cache.shape[1:]) == (1, PAGE, Dk),
+              "latent_prepare: cache layout")
+        _need(norm_weight is not None and norm_weight.dtype == torch.float32 and norm_weight.numel() == kv_rank, "latent_prepare: norm weight")
+    _need(rot_dims == 0 or (inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dims // 2),
+          "latent_prepare: one frequency per pair")
+    _check(lib("latent").kl_latent_prepare(
+        _ptr(proj), ctypes.c_longlong(proj.stride(0)), q_col, -1 if kv_col is None else kv_col, _ptr(norm_weight), ctypes.c_float(eps),
+        _ptr(inv_freq), rot_dims, ctypes.c_float(mscale), int(bool(interleaved)), _ptr(positions), _ptr(token_slot),
+        _ptr(block_table), 0 if block_table is None else block_table.shape[1], _ptr(cache if kv_col is not None else None), _ptr(qfull),
+        n_tokens, heads, dim, rot_dim, kv_rank, dtype_code(proj.dtype), _stream()), "latent_prepare")
+
+
+def latent_attention(qfull: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, step, heads: int,
+                     key_dim: int, value_dim: int, scale: float, sink: Optional[torch.Tensor] = None) -> None:
+    """Causal attention of ``heads`` query heads [key_dim] over the one key head of the cache's rows, the values being
+    each row's first ``value_dim`` columns; out [tokens, heads * value_dim]."""
+    attention_simt(qfull, heads * key_dim, out, cache, cache, block_table, step.positions, step.token_slot, step.n_tokens,
+                   heads, 1, key_dim, scale, 0, value_dim=value_dim, sink=sink)
+
+
+# --------------------------------------------------------------------------- gated linear recurrence
+
+def causal_conv(proj: torch.Tensor, x_col: int, x_bias: Optional[torch.Tensor], weight: torch.Tensor, bias: Optional[torch.Tensor],
+                state: torch.Tensor, step, width: int, out: torch.Tensor) -> None:
+    """out[t, c] (float32) = bias[c] + sum_k weight[c, k] * x[t - (taps - 1 - k), c], x = proj[:, x_col + c] + x_bias[c];
+    inputs before the step come from ``state`` [slots, width * taps] (S, then the last taps - 1 inputs)."""
+    _cuda(proj, x_bias, weight, bias, state, out)
+    taps = weight.shape[1]
+    _need(weight.dtype == torch.float32 and weight.is_contiguous() and weight.shape[0] == width, "causal_conv: weight [width, taps]")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1 and state.shape[1] >= width * taps, "causal_conv: state")
+    _need(out.dtype == torch.float32 and out.is_contiguous() and out.shape[1] == width and out.shape[0] >= step.n_tokens, "causal_conv: out")
+    _need(proj.dim() == 2 and proj.stride(1) == 1 and x_col + width <= proj.shape[1], "causal_conv: projections")
+    for b in (x_bias, bias):
+        _need(b is None or (b.dtype == torch.float32 and b.numel() == width and b.is_contiguous()), "causal_conv: bias")
+    _check(lib("linear_recurrence").kl_causal_conv(
+        _ptr(proj), ctypes.c_longlong(proj.stride(0)), x_col, _ptr(x_bias), _ptr(weight), _ptr(bias), taps, _ptr(state),
+        ctypes.c_longlong(state.stride(0)), _ptr(step.cu_tokens), _ptr(step.seq_slots), _ptr(step.seq_new), step.n_seqs, step.max_new,
+        width, _ptr(out), dtype_code(proj.dtype), _stream()), "causal_conv")
+
+
+def rglru_gate(gates: torch.Tensor, u: torch.Tensor, r_bias: torch.Tensor, i_bias: torch.Tensor, softplus_lambda: torch.Tensor,
+               decay_scale: float, n_tokens: int, width: int, block: int) -> None:
+    """In place on ``gates`` float32 [tokens, blocks, 2 block] (recurrence gate then input gate pre-activations of
+    every block): a = exp(-decay_scale * sigmoid(r) * softplus_lambda) over r, sqrt(1 - a^2) * sigmoid(i) * u over i."""
+    _cuda(gates, u, r_bias, i_bias, softplus_lambda)
+    for t in (gates, u, r_bias, i_bias, softplus_lambda):
+        _need(t.dtype == torch.float32 and t.is_contiguous(), "rglru_gate: float32 tensors")
+    _need(gates.shape[0] >= n_tokens and gates.shape[1] == 2 * width and u.shape[1] == width and width % block == 0, "rglru_gate: shapes")
+    _check(lib("linear_recurrence").kl_rglru_gate(_ptr(gates), _ptr(u), _ptr(r_bias), _ptr(i_bias), _ptr(softplus_lambda),
+                                                  ctypes.c_float(decay_scale), n_tokens, width, block, _stream()), "rglru_gate")
+
+
+def linear_scan(gates: torch.Tensor, block: int, proj: torch.Tensor, y_col: int, x_col: int, y_bias: Optional[torch.Tensor],
+                x_bias: Optional[torch.Tensor], taps: int, state: torch.Tensor, step, width: int, out: torch.Tensor) -> None:
+    """S_t = a_t S_(t-1) + b_t per channel from the slot's state, a and b as ``rglru_gate`` left them;
+    out[t, c] = S_t * gelu_tanh(proj[t, y_col + c] + y_bias[c]); the state (S and the convolution's last inputs) moves on."""
+    _cuda(gates, proj, y_bias, x_bias, state, out)
+    _need(gates.dtype == torch.float32 and gates.is_contiguous() and gates.shape[1] == 2 * width, "linear_scan: gates")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1 and state.shape[1] >= width * taps, "linear_scan: state")
+    _need(out.is_contiguous() and out.dtype == proj.dtype and out.shape[1] == width and out.shape[0] >= step.n_tokens, "linear_scan: out")
+    _need(proj.stride(1) == 1 and max(y_col, x_col) + width <= proj.shape[1], "linear_scan: projections")
+    _check(lib("linear_recurrence").kl_linear_scan(
+        _ptr(gates), block, _ptr(proj), ctypes.c_longlong(proj.stride(0)), y_col, x_col, _ptr(y_bias), _ptr(x_bias), taps, _ptr(state),
+        ctypes.c_longlong(state.stride(0)), _ptr(step.cu_tokens), _ptr(step.seq_slots), _ptr(step.seq_new), step.n_seqs, width,
+        _ptr(out), dtype_code(proj.dtype), _stream()), "linear_scan")
 
 
 # --------------------------------------------------------------------------- matrix products

@@ -1,0 +1,74 @@
+"""A mixture of experts as a feed-forward: a router, a grouped product per projection, a weighted sum."""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..config.spec import PartSpec
+from ..csrc import ops
+from ..weights.loader import TensorDecl
+from .base import FeedForward, NormedLazy, Runtime, StepContext, register_feed_forward
+from .linear import Linear
+
+
+@register_feed_forward("moe")
+class MoEFeedForward(FeedForward):
+    """``experts`` small gated feed-forwards of which every token uses ``top``:
+
+        z = W_router n (32-bit);  s = softmax(z) over all experts;  the ``top`` largest s are chosen
+        expert e:  g = min(W_gate[e] n, limit), u = clamp(W_up[e] n, -limit, limit),
+                   f_e = W_down[e] (g * sigmoid(alpha * g) * (u + shift))          (no clamp when limit is None)
+        out = sum over the chosen e of s_e * f_e     (the weights are divided by their sum if ``renormalise``)
+
+    Routing stays on the device (``ops.moe_route`` / ``moe_plan``): the (token, choice) pairs are sorted by
+    expert into a list padded to whole tiles, one grouped product makes gate, up and the activation for
+    the whole list, one more the down projection, and ``moe_combine`` adds each token's results in the
+    order of its choices in 32 bits.  The result is handed on as one float32 piece.
+
+    Spec: ``hidden_size``, ``experts``, ``top``, ``expert_size``, ``limit``, ``alpha``, ``shift``, ``renormalise``,
+    ``names``: router and, with ``{e}`` for the expert's number, gate, up, down.  KuiperLLama's only feed-forward is
+    the dense SwiGLU (kuiper/source/model/llama3.cpp:692-718)."""
+
+    @classmethod
+    def manifest(cls, spec: PartSpec, prefix: str) -> Dict[str, TensorDecl]:
+        hid, E, ff, n = spec["hidden_size"], spec["experts"], spec["expert_size"], spec["names"]
+        m = {prefix + n["router"]: TensorDecl((E, hid))}
+        for e in range(E):
+            m[prefix + n["gate"].format(e=e)] = TensorDecl((ff, hid))
+            m[prefix + n["up"].format(e=e)] = TensorDecl((ff, hid))
+            m[prefix + n["down"].format(e=e)] = TensorDecl((hid, ff))
+        return m
+
+    def __init__(self, spec, prefix, tensors, runtime: Runtime):
+        super().__init__(spec, prefix, tensors, runtime)
+        self.hidden, self.E, self.top, self.ff = (int(spec[k]) for k in ("hidden_size", "experts", "top", "expert_size"))
+        if not 0 < self.top <= self.E <= ops.MOE_MAX_EXPERTS:
+            raise ValueError(f"{self.top} of {self.E} experts: the routing kernels take up to {ops.MOE_MAX_EXPERTS} experts")
+        limit = spec.get("limit")
+        self.activation = (float(limit) if limit is not None else 0.0, float(spec.get("alpha", 1.0)), float(spec.get("shift", 0.0)))
+        self.renormalise = bool(spec.get("renormalise", False))
+        n = spec["names"]
+        dev, dt = runtime.device, runtime.dtype
+        get = lambda key, e: tensors[prefix + n[key].format(e=e)].to(device=dev, dtype=dt)
+        self.router = Linear(tensors[prefix + n["router"]], runtime)
+        # [experts, 2 ff, hidden]: an expert's gate rows, then its up rows; [experts, hidden, ff]
+        self.gate_up = torch.stack([torch.cat([get("gate", e), get("up", e)], dim=0) for e in range(self.E)]).contiguous()
+        self.down = torch.stack([get("down", e) for e in range(self.E)]).contiguous()
+
+    def forward(self, x, step: StepContext):
+        if isinstance(x, NormedLazy):
+            x = x.dense()
+        n, dev, dt = step.n_tokens, x.device, self.runtime.dtype
+        logits = self.router.forward(x, out_dtype=torch.float32)
+        choice, weight = ops.moe_route(logits, self.top, self.renormalise)
+        tile = 16 if n * self.top <= 16 * self.E else 64
+        pair_pos, list_rows, tile_group = ops.moe_plan(choice, self.E, tile, step.token_slot)
+        cap = list_rows.numel()
+        act = torch.empty((cap, self.ff), dtype=dt, device=dev)
+        ops.grouped_gemm(x, self.gate_up, act, a_rows=list_rows, tile_group=tile_group, tile_rows=tile, gated=self.activation)
+        res = torch.empty((cap, self.hidden), dtype=dt, device=dev)
+        ops.grouped_gemm(act, self.down, res, a_rows=None, tile_group=tile_group, tile_rows=tile)
+        out = torch.empty((1, n, self.hidden), dtype=torch.float32, device=dev)
+        ops.moe_combine(res, pair_pos, weight, out[0])
+        return out

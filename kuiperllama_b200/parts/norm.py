@@ -15,17 +15,21 @@ from .base import Accumulated, Norm, NormedLazy, PostNormed, Runtime, register_n
 class RMSNorm(Norm):
     """out = w * x * rsqrt(mean(x^2) + eps) on x = residual + delta, statistics in 32 bits
     (ExiledOfCode/KuiperLLama rmsnorm_kernel.cu:70-106; the add is its add_kernel.cu:4-12,
-    fused here).  ``size``, ``eps`` and the tensor's ``name`` come from the spec."""
+    fused here).  ``size``, ``eps`` and the tensor's ``name`` come from the spec; with ``weight_offset`` c the
+    stored tensor is w - c (a weight kept around zero: the norm multiplies by c + stored)."""
 
     @classmethod
     def manifest(cls, spec: PartSpec, prefix: str) -> Dict[str, TensorDecl]:
-        return {prefix + spec["name"]: TensorDecl((spec["size"],), role="vector", init="one_plus_normal")}
+        init = "normal" if spec.get("weight_offset") else "one_plus_normal"
+        return {prefix + spec["name"]: TensorDecl((spec["size"],), role="vector", init=init)}
 
     def __init__(self, spec, prefix, tensors, runtime: Runtime):
         super().__init__(spec, prefix, tensors, runtime)
         self.size = int(spec["size"])
         self.eps = float(spec["eps"])
         self.weight = tensors[prefix + spec["name"]].to(device=runtime.device, dtype=torch.float32).contiguous()
+        if spec.get("weight_offset"):
+            self.weight = (self.weight + float(spec["weight_offset"])).contiguous()      # exact for a bfloat16 checkpoint: 32-bit sum
 
     accepts_accumulated = True
 
@@ -73,6 +77,24 @@ def add_to_stream(residual: torch.Tensor, delta) -> None:
         ops.norm_chain(residual, delta.value, None, None, None, 0.0, "layernorm", gate=delta.gate, gate_bias=delta.gate_bias, post=post)
     else:
         ops.norm_chain(residual, delta, None, None, None, 0.0, "layernorm")
+
+
+@register_norm("none")
+class NoNorm(Norm):
+    """No norm before a sublayer: the sublayer reads the stream itself (in the compute dtype).  It still is the
+    place where what is pending gets added, so a block whose sublayers are normed only AFTER they ran
+    (x += norm(sublayer(x))) is the sandwich block with this part in front.  No tensors; spec: ``size``."""
+
+    kind = "none"
+    weight = None
+    eps = 0.0
+
+    def __init__(self, spec, prefix, tensors, runtime: Runtime):
+        super().__init__(spec, prefix, tensors, runtime)
+        self.size = int(spec["size"])
+
+    def forward(self, residual: torch.Tensor, delta, n_rows: int, rows: Optional[torch.Tensor] = None):
+        return chain_forward(self, residual, delta, rows)
 
 
 @register_norm("layernorm")

@@ -135,3 +135,71 @@ class GatedDeltaMixer(Mixer):
         gated = torch.empty((n, self.H * self.dv), dtype=self.runtime.dtype, device=x.device)
         ops.head_rmsnorm_gate(o, self.inputs.view("g"), self.norm_weight, gated, self.H, self.dv, self.norm_eps)
         return self.o.forward(gated, allow_partials=True)
+
+
+@register_mixer("rglru")
+class RGLRUMixer(Mixer):
+    """The recurrent block with a real-gated linear recurrent unit (De et al., "Griffin: Mixing Gated Linear
+    Recurrences with Local Attention for Efficient Language Models", 2024).  Two branches of ``width``:
+
+        y = gelu_tanh(Wy n + by);   u = conv(Wx n + bx)    (a causal convolution per channel over ``conv`` inputs, with bias)
+        per block b of width / blocks channels:  r = sigmoid(Ra[b] u_b + ra_b),  i = sigmoid(Ri[b] u_b + ri_b)
+        a = exp(-decay_scale * r * softplus(lambda));   S_t = a S_(t-1) + sqrt(1 - a^2) * i * u;   out = Wo (S_t * y)
+
+    S starts at zero and the first token takes no other path.  The slot's state is float32: S [width], then
+    the convolution's last conv - 1 inputs.  u, both gates, a and S are 32-bit in every run: the gate matrices
+    are held in float32 and multiplied by the grouped product's float32 instance.  Spec: ``hidden_size``,
+    ``width``, ``blocks``, ``conv``, ``decay_scale`` and ``names`` (y, x, y_bias, x_bias, conv, conv_bias, ra,
+    ra_bias, ri, ri_bias, lam, o).  KuiperLLama has no recurrent mixer (its mixer is mha_kernel.cu:61,74-106)."""
+
+    @classmethod
+    def manifest(cls, spec: PartSpec, prefix: str) -> Dict[str, TensorDecl]:
+        hid, w, B, K, n = (spec[k] for k in ("hidden_size", "width", "blocks", "conv", "names"))
+        bs = w // B
+        vec = lambda shape: TensorDecl(shape, role="vector")
+        return {prefix + n["y"]: TensorDecl((w, hid)), prefix + n["x"]: TensorDecl((w, hid)), prefix + n["o"]: TensorDecl((hid, w)),
+                prefix + n["y_bias"]: vec((w,)), prefix + n["x_bias"]: vec((w,)), prefix + n["conv"]: vec((w, K)),
+                prefix + n["conv_bias"]: vec((w,)), prefix + n["ra"]: vec((B, bs, bs)), prefix + n["ra_bias"]: vec((B, bs)),
+                prefix + n["ri"]: vec((B, bs, bs)), prefix + n["ri_bias"]: vec((B, bs)), prefix + n["lam"]: vec((w,))}
+
+    def __init__(self, spec, prefix, tensors, runtime: Runtime, position: Optional[PositionEncoding] = None):
+        super().__init__(spec, prefix, tensors, runtime, position)
+        self.hidden, self.width, self.blocks, self.taps = (int(spec[k]) for k in ("hidden_size", "width", "blocks", "conv"))
+        if self.blocks < 1 or self.width % self.blocks:
+            raise ValueError(f"a width of {self.width} does not split into {self.blocks} equal blocks")
+        if not 1 <= self.taps <= 16:
+            raise ValueError(f"the convolution kernel takes 1 to 16 taps, got {self.taps}")
+        self.block = self.width // self.blocks
+        self.decay_scale = float(spec["decay_scale"])
+        n = spec["names"]
+        self.inputs = StackedInput(runtime)
+        self.inputs.add("y", tensors[prefix + n["y"]])
+        self.inputs.add("x", tensors[prefix + n["x"]])
+        self.o = Linear(tensors[prefix + n["o"]], runtime)
+        f32 = lambda name: tensors[prefix + name].to(device=runtime.device, dtype=torch.float32).contiguous()
+        self.y_bias, self.x_bias, self.conv_weight, self.conv_bias = f32(n["y_bias"]), f32(n["x_bias"]), f32(n["conv"]), f32(n["conv_bias"])
+        # both gates of a block from one product: [blocks, 2 block, block], recurrence-gate rows then input-gate rows
+        self.gate_weight = torch.cat([f32(n["ra"]), f32(n["ri"])], dim=1).contiguous()
+        self.ra_bias, self.ri_bias = f32(n["ra_bias"]).reshape(-1), f32(n["ri_bias"]).reshape(-1)
+        self.softplus_lambda = torch.nn.functional.softplus(f32(n["lam"])).contiguous()      # made once, in float32
+
+    def state_request(self) -> Optional[StateRequest]:
+        return StateRequest((self.width * self.taps,), torch.float32)
+
+    def forward(self, x, step: StepContext, cache: CacheView) -> torch.Tensor:
+        if isinstance(x, NormedLazy):
+            x = x.dense()
+        n, w, dev = step.n_tokens, self.width, x.device
+        proj = self.inputs.forward(x)
+        y_col, x_col = self.inputs.column("y"), self.inputs.column("x")
+        # rows that belong to no sequence (a small step's padding) are not written by the kernels: keep them defined
+        make = torch.empty if n == step.n_seqs else torch.zeros
+        u = make((n, w), dtype=torch.float32, device=dev)
+        ops.causal_conv(proj, x_col, self.x_bias, self.conv_weight, self.conv_bias, cache.state, step, w, u)
+        gates = torch.empty((n, 2 * w), dtype=torch.float32, device=dev)
+        ops.grouped_gemm(u, self.gate_weight, gates, a_group_stride=self.block, out_group_stride=2 * self.block, rows=n,
+                         tile_rows=16 if n <= 16 else 64)
+        ops.rglru_gate(gates, u, self.ra_bias, self.ri_bias, self.softplus_lambda, self.decay_scale, n, w, self.block)
+        mixed = make((n, w), dtype=self.runtime.dtype, device=dev)
+        ops.linear_scan(gates, self.block, proj, y_col, x_col, self.y_bias, self.x_bias, self.taps, cache.state, step, w, mixed)
+        return self.o.forward(mixed, allow_partials=True)
