@@ -40,6 +40,14 @@ def pytest_terminal_summary(terminalreporter):
         terminalreporter.write_line("largest observed error / largest reference magnitude:")
         for (dtype, what), v in sorted(OBSERVED.items()):
             terminalreporter.write_line(f"  {dtype:9s} {what:24s} {v:.3e}")
+    try:
+        from munadra_helpers import OBSERVED as MUNADRA
+    except Exception:
+        return
+    if MUNADRA:
+        terminalreporter.write_line("Munadra: largest row error / the row's spread:")
+        for (dtype, what), v in sorted(MUNADRA.items()):
+            terminalreporter.write_line(f"  {dtype:9s} {what:24s} {v:.3e}")
 
 
 @pytest.fixture(scope="session")

@@ -20,7 +20,7 @@ F = torch.float64
 
 
 def t64(a) -> torch.Tensor:
-    return torch.as_tensor(a).to(F)
+    return torch.as_tensor(a, dtype=F)
 
 
 def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float, offset: float = 0.0) -> torch.Tensor:
