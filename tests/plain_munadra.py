@@ -76,9 +76,10 @@ def latent_keys(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, m: dict, ep
     return c, kr
 
 
-def latent_attention(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, m: dict, eps: float,
-                     shared: Optional[Tuple[torch.Tensor, torch.Tensor]] = None):
-    """h [T, width] -> ([T, width], (c, k_rot)).  ``shared``: another layer's latent and rotated key part."""
+def latent_attention_weights(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, m: dict, eps: float,
+                             shared: Optional[Tuple[torch.Tensor, torch.Tensor]] = None):
+    """The softmax weights [H, T, T] (rows sum to less than 1: the sink takes its share), the values [T, H, vdim]
+    and (c, k_rot)."""
     T = h.shape[0]
     H, d, rd, dv, r = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
     c, kr = shared if shared is not None else latent_keys(h, W, p, m, eps)
@@ -95,10 +96,17 @@ def latent_attention(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, m: dic
     sink = t64(W[p + "sink"])                                            # one more term in every denominator
     top = torch.maximum(s.max(dim=-1).values, sink[:, None])
     e = torch.exp(s - top[..., None])
-    w = e / (e.sum(dim=-1) + torch.exp(sink[:, None] - top))[..., None]
+    return e / (e.sum(dim=-1) + torch.exp(sink[:, None] - top))[..., None], v, (c, kr)
+
+
+def latent_attention(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, m: dict, eps: float,
+                     shared: Optional[Tuple[torch.Tensor, torch.Tensor]] = None):
+    """h [T, width] -> ([T, width], (c, k_rot)).  ``shared``: another layer's latent and rotated key part."""
+    T = h.shape[0]
+    w, v, latent = latent_attention_weights(h, W, p, m, eps, shared)
     o = torch.einsum("hij,jhd->ihd", w, v)
     o = o * torch.sigmoid(h @ t64(W[p + "g"]).T)[..., None]
-    return o.reshape(T, H * dv) @ t64(W[p + "o"]).T, (c, kr)
+    return o.reshape(T, m["heads"] * m["vdim"]) @ t64(W[p + "o"]).T, latent
 
 
 def rglru(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, m: dict) -> torch.Tensor:
