@@ -4,7 +4,7 @@ B200, and the two other workloads of the same family (Llama-2-7B shape with ragg
 Llama-3.2-1B shape with temperature sampling).
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--batch B] [--impl reference] [--no-points]
-    python bench.py --compare terolix [--sizes 1b,8b-8-layers]      (another design beside Llama; see compare_designs)
+    python bench.py --compare terolix|munadra [--sizes 1b,8b-8-layers]      (another design beside Llama; see compare_designs)
 
 A "step" is one decode step of a batch (default 8 sequences that each hold a 512-token
 prompt, context limit 4096).  One JSON line is printed:
@@ -369,6 +369,33 @@ def terolix_config(width, layers, heads, kv_heads, head_dim, ff, vocab):
             "layers": [dict(kinds[order[i % 4]], mlp={"kind": "dense", "ff": ff}) for i in range(layers)]}
 
 
+def munadra_config(width, layers, heads, head_dim, vocab):
+    """A Munadra model of ``layers`` layers in groups of four: latent attention that makes the latent (dense
+    feed-forward), a recurrent block, and two latent-attention layers that read the first one's rows (mixtures of
+    16 experts of which a token uses 4, so that a token's feed-forward work equals the Llama shape's: 4 x 3 W (I / 4)).
+    Heads of ``head_dim`` unrotated and half as many rotated dimensions, a latent of 256."""
+    inter = COMPARE_INTER[width]
+    rot = {"base": 500000.0, "dims": head_dim // 2, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}
+    att = lambda src: {"type": "latent_attention", "mixer": dict(
+        {"heads": heads, "dim": head_dim, "rot_dim": head_dim // 2, "vdim": head_dim, "kv_rank": 256, "scale": (1.5 * head_dim) ** -0.5, "rot": rot},
+        **({} if src is None else {"kv_from": src}))}
+    moe = {"kind": "moe", "router": {"experts": 16, "top": 4}, "expert": {"ff": inter // 4, "limit": 7.0}}
+    out = []
+    for i in range(layers):
+        first = i - i % 4
+        if i % 4 == 0:
+            out.append(dict(att(None), mlp={"kind": "dense", "ff": inter}))
+        elif i % 4 == 1:
+            out.append({"type": "rglru", "mixer": {"width": width, "blocks": width // 128, "conv": 4}, "mlp": moe})
+        else:
+            out.append(dict(att(first), mlp=moe))
+    return {"architecture": "Munadra", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "logit_scale": 1.0, "logit_softcap": 30.0, "layers": out}
+
+
+COMPARE_INTER = {2048: 8192, 4096: 14336}
+
+
 # Pairs of equal size: the Llama shape (tied classifier, a vocabulary of 32,000 so that the layers carry the
 # step) and a Terolix model of the same width, depth, heads and head size whose feed-forward is as large
 # as the Llama one's once the two gates of a layer are counted with it (2 W F + 2 W^2 = 3 W I).
@@ -379,7 +406,7 @@ COMPARE_SIZES = {
 
 
 def compare_designs(args):
-    """``--compare terolix``: prefill (one prompt of 2,048 tokens) and decode (8 and 64 sequences after
+    """``--compare terolix`` (or ``munadra``): prefill (one prompt of 2,048 tokens) and decode (8 and 64 sequences after
     512-token prompts, CUDA graphs) of Terolix beside the Llama decoder at equal size, random weights,
     bfloat16.  Rates in tokens a second; ``hbm_frac`` is the weights' bytes over the decode step's time
     over the copy peak, ``tc_frac`` the prefill's matrix-product flops over its time over the bf16 peak."""
@@ -397,13 +424,19 @@ def compare_designs(args):
         llama = dict(LLAMA31_8B, hidden_size=z["width"], intermediate_size=z["inter"], num_hidden_layers=z["layers"],
                      num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"], head_dim=z["head_dim"], vocab_size=vocab,
                      tie_word_embeddings=True)
-        tero = terolix_config(z["width"], z["layers"], z["heads"], z["kv_heads"], z["head_dim"], z["ff"], vocab)
+        if args.compare == "munadra":
+            other = munadra_config(z["width"], z["layers"], z["heads"], z["head_dim"], vocab)
+        else:
+            other = terolix_config(z["width"], z["layers"], z["heads"], z["kv_heads"], z["head_dim"], z["ff"], vocab)
         out[name] = {}
-        for design, cfg in (("llama", llama), ("terolix", tero)):
+        for design, cfg in (("llama", llama), (args.compare, other)):
             model = kl.random_model(config_from_dict(cfg), seed=0, dtype="bfloat16", device="cuda:0")
             infer = kl.Inference(model, max_tokens=64 * CONTEXT, max_batch=64, max_seq_len=CONTEXT)
             wbytes = model.weight_bytes()
             matrix_params = wbytes / 2 - vocab * z["width"]
+            if design == "munadra":          # a token uses 4 of a layer's 16 experts: count what it multiplies by
+                moe_layers = sum(1 for l in cfg["layers"] if l["mlp"]["kind"] == "moe")
+                matrix_params -= moe_layers * 12 * 3 * z["width"] * (COMPARE_INTER[z["width"]] // 4)
             t = time_prefill(infer, warmup=3, repeats=5, seed=2, checks=checks)
             r = {"weight_gb": round(wbytes / 1e9, 3), "prefill_tokens_per_s": round(PREFILL_LEN / t, 1), "prefill_ms": round(t * 1e3, 3),
                  "prefill_tc_frac": round(2 * PREFILL_LEN * matrix_params / t / (pk["bf16_tflops"] * 1e12), 4)}
@@ -417,9 +450,9 @@ def compare_designs(args):
             out[name][design] = r
             del infer, model
             torch.cuda.empty_cache()
-        a, b = out[name]["terolix"], out[name]["llama"]
-        out[name]["terolix_over_llama"] = {k: round(a[k] / b[k], 3) for k in a if k.endswith("tokens_per_s")}
-    print(json.dumps({"metric": "prefill and decode tok/s of Terolix beside Llama at equal size, bf16, random weights",
+        a, b = out[name][args.compare], out[name]["llama"]
+        out[name][args.compare + "_over_llama"] = {k: round(a[k] / b[k], 3) for k in a if k.endswith("tokens_per_s")}
+    print(json.dumps({"metric": f"prefill and decode tok/s of {args.compare.capitalize()} beside Llama at equal size, bf16, random weights",
                       "impl": "ours", "n_gpus": 1, "dtype": "bf16", "data": "synthetic: random weights N(0, 0.02), uniform random token ids",
                       "prompt_len": PROMPT_LEN, "prefill_len": PREFILL_LEN, "peaks": pk["source"], "sizes": out,
                       "clocks": clocks.stop(), "checks": checks}))
@@ -451,7 +484,7 @@ def main():
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--no-points", action="store_true",
                     help="only the headline: skip the prefill, the batch 1, 64 and 128 points and the two other workloads")
-    ap.add_argument("--compare", default=None, choices=["terolix"],
+    ap.add_argument("--compare", default=None, choices=["terolix", "munadra"],
                     help="instead of the default workload: this design beside Llama at equal size (prefill and decode rates)")
     ap.add_argument("--sizes", default="", help="with --compare: which of the sizes to run, with commas (default: all)")
     args = ap.parse_args()

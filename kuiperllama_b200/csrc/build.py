@@ -40,6 +40,7 @@ SOURCES: Dict[str, str] = {
     "grouped_gemm": "grouped_gemm.cu",
     "moe": "moe.cu",
     "latent": "latent.cu",
+    "attention_latent": "attention_latent.cu",
     "linear_recurrence": "linear_recurrence.cu",
 }
 HEADERS: List[str] = ["common.cuh", "tcgen05.cuh", "tma_host.cuh", "attention_decode_noalloc.h"]

@@ -58,6 +58,15 @@ struct GemmArgs {
     int* sink_counters;       //   128 columns per row in sink_ss[tile][64]; counters are zero between launches
     const float* sink_w;      // with sink: the next norm's weight [rows_a], and where bf16(x * w) of the new
     __nv_bfloat16* sink_scaled;   //   rows goes [rows_b, rows_a] (the next product's activations); may be null
+    // Tokens-as-rows only: a grouped product.  The token rows are a list sorted by group in which every
+    // tile of 128 rows lies in one group; tile_group[token tile] names it (-1: the tile is skipped), and
+    // the group's weights are the rows group * group_rows .. of the B operand (rows_b counts one group's).
+    const int* tile_group;
+    int group_rows;
+    // With swiglu and act_custom: min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u, -limit, limit) + shift),
+    // no clamp when limit <= 0 (act_custom 0: silu(g) * u).
+    int act_custom;
+    float act_limit, act_alpha, act_shift;
 };
 
 // Tile order for tokens-as-rows: all the feature tiles of a group of TC_GROUP_M token tiles
@@ -77,6 +86,11 @@ __device__ __forceinline__ void tile_of(int id, int tiles_m, int tiles_n, int& t
 // division takes a slow path whenever exp(-g) overflows, and this runs 16,384 times per tile beside
 // the products).  For g far below zero the denominator is huge or infinite and the quotient 0, as it should be.
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
+__device__ __forceinline__ float gated_mul(const GemmArgs& args, float g, float u) {
+    if (!args.act_custom) return silu_mul(g, u);
+    if (args.act_limit > 0.f) { g = fminf(g, args.act_limit); u = fminf(fmaxf(u, -args.act_limit), args.act_limit); }
+    return __fdividef(g, 1.0f + __expf(-args.act_alpha * g)) * (u + args.act_shift);
+}
 
 // Tokens-as-rows: 32 accumulator columns of one token row to the output (columns n0 .. n0 + 31).
 __device__ __forceinline__ void store_row_chunk(const GemmArgs& args, int row, int n0, const uint32_t (&r)[32]) {
@@ -123,8 +137,8 @@ __device__ __forceinline__ void store_row_chunk_swiglu(const GemmArgs& args, int
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 __nv_bfloat162 pr = __floats2bfloat162_rn(
-                    silu_mul(__uint_as_float(rg[j + 2 * e]), __uint_as_float(ru[j + 2 * e])),
-                    silu_mul(__uint_as_float(rg[j + 2 * e + 1]), __uint_as_float(ru[j + 2 * e + 1])));
+                    gated_mul(args, __uint_as_float(rg[j + 2 * e]), __uint_as_float(ru[j + 2 * e])),
+                    gated_mul(args, __uint_as_float(rg[j + 2 * e + 1]), __uint_as_float(ru[j + 2 * e + 1])));
                 w[e] = *reinterpret_cast<uint32_t*>(&pr);
             }
             *reinterpret_cast<uint4*>(o + j) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -132,7 +146,7 @@ __device__ __forceinline__ void store_row_chunk_swiglu(const GemmArgs& args, int
     } else {
         for (int j = 0; j < 32; ++j)
             if (f0 + j < half_n)
-                o[j] = __float2bfloat16_rn(silu_mul(__uint_as_float(rg[j]), __uint_as_float(ru[j])));
+                o[j] = __float2bfloat16_rn(gated_mul(args, __uint_as_float(rg[j]), __uint_as_float(ru[j])));
     }
 }
 
@@ -188,9 +202,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (elect_one()) {
             int issued = 0;                                   // k blocks requested so far, over all tiles
             bool ok = true;
+            if (!WEIGHT_ROWS && args.tile_group != nullptr) pdl_wait();      // the list of groups is written by a kernel ahead
             for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
                 int tile_a, tile_b;
                 tile_at(t, tile_a, tile_b);
+                int b_row = tile_b * BN;                      // first row of the B operand's tile
+                if (!WEIGHT_ROWS && args.tile_group != nullptr) {
+                    const int g = args.tile_group[tile_a];
+                    if (g < 0) continue;
+                    b_row += g * args.group_rows;
+                }
                 int first = 0;
                 if (issued == 0) {
                     // Weights are written by no kernel, so their tiles for the first stages are requested
@@ -199,7 +220,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     for (int i = 0; i < pre; ++i) {
                         mbar_expect_tx(&full[i], A_BYTES + B_BYTES);
                         if constexpr (WEIGHT_ROWS) tma_load_2d(tiles_a + i * A_BYTES, &map_a, &full[i], (kb0 + i) * TC_BK, tile_a * TC_BM);
-                        else tma_load_2d(tiles_b + i * B_BYTES, &map_b, &full[i], (kb0 + i) * TC_BK, tile_b * BN);
+                        else tma_load_2d(tiles_b + i * B_BYTES, &map_b, &full[i], (kb0 + i) * TC_BK, b_row);
                     }
                     pdl_wait();
                     for (int i = 0; i < pre; ++i) {
@@ -213,7 +234,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     if (issued >= STAGES && !mbar_wait(&empty[s], ((issued / STAGES) - 1) & 1, abort_flag, args.status, 1)) { ok = false; break; }
                     mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
                     tma_load_2d(tiles_a + s * A_BYTES, &map_a, &full[s], (kb0 + i) * TC_BK, tile_a * TC_BM);
-                    tma_load_2d(tiles_b + s * B_BYTES, &map_b, &full[s], (kb0 + i) * TC_BK, tile_b * BN);
+                    tma_load_2d(tiles_b + s * B_BYTES, &map_b, &full[s], (kb0 + i) * TC_BK, b_row);
                     ++issued;
                 }
             }
@@ -235,6 +256,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             bool ok = true;
             int it = 0, lt = 0;                               // k blocks consumed, tiles done (both over all tiles)
             for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++lt) {
+                if (!WEIGHT_ROWS && args.tile_group != nullptr) {
+                    int tile_a, tile_b;
+                    tile_at(t, tile_a, tile_b);
+                    if (args.tile_group[tile_a] < 0) { --lt; continue; }      // a skipped tile takes no accumulator
+                }
                 const int buf = lt & 1, use = lt >> 1;
                 if (use > 0) {                                // the epilogue must have read this accumulator out
                     ok = mbar_wait(&acc_empty[buf], (use - 1) & 1, abort_flag, args.status, 4);
@@ -283,6 +309,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++lt) {
         int tile_a, tile_b;
         tile_at(t, tile_a, tile_b);
+        if (!WEIGHT_ROWS && args.tile_group != nullptr && args.tile_group[tile_a] < 0) { --lt; continue; }
         const int buf = lt & 1;
         const bool ok = mbar_wait(&acc_full[buf], (lt >> 1) & 1, abort_flag, args.status, 3) && !*abort_flag;
         tc_fence_after();
@@ -710,6 +737,35 @@ KL_API int kl_gemm_tcgen05(const void* a, long long lda, const void* w, long lon
     const int tiles = tiles_m * tiles_n;
     const int grid_x = min(tiles, sms);               // one CTA per SM walks the tiles
     dim3 grid(grid_x, 1, 1);
+    return launch<256, 4, false>(ma, mb, args, grid, stream);
+}
+
+// A grouped product: out[p, :] = a[p, :] * w[g(p)]^T for the places p of a list sorted by group in which
+// every tile of 128 places lies in one group (tile_group[tile], -1: skipped; M = tiles * 128 places).
+// w holds `groups` matrices of n_rows rows each, one after the other.  gated: a group's rows alternate
+// 64 gate rows and 64 up rows and the result has n_rows / 2 columns, with the activation of
+// (limit, alpha, shift) (see GemmArgs).  Single CTAs on tiles of 128 x 256.
+KL_API int kl_gemm_tcgen05_grouped(const void* a, long long lda, const void* w, long long ldw, void* out, long long ldo, int M,
+                                   int n_rows, int K, int groups, const int* tile_group, int gated, float limit, float alpha,
+                                   float shift, int* status, cudaStream_t stream) {
+    if (M <= 0 || n_rows <= 0 || groups <= 0) return KL_OK;
+    if (M % TC_BM || tile_group == nullptr || (gated && n_rows % 128)) return KL_ERR_BAD_SIZE;
+    if (!aligned_operand(a, lda, K) || !aligned_operand(w, ldw, K)) return KL_ERR_BAD_ALIGN;
+    if ((long long)groups * n_rows > 0x7fffffffLL) return KL_ERR_BAD_SIZE;
+    CUtensorMap ma, mb;
+    int rc;
+    if ((rc = make_map(&ma, a, M, K, lda, TC_BM)) != KL_OK) return rc;
+    if ((rc = make_map(&mb, w, groups * n_rows, K, ldw, 256)) != KL_OK) return rc;
+    const int tiles_m = M / TC_BM, tiles_n = (n_rows + 255) / 256;
+    GemmArgs args{out, ldo, 0, M, n_rows, (K + TC_BK - 1) / TC_BK, 0, status, tiles_m, tiles_n, gated};
+    args.tile_group = tile_group;
+    args.group_rows = n_rows;
+    args.act_custom = gated;
+    args.act_limit = limit; args.act_alpha = alpha; args.act_shift = shift;
+    if ((long long)tiles_m * tiles_n > 0x7fffffffLL) return KL_ERR_BAD_SIZE;
+    const int sms = kl::sm_count();
+    if (sms <= 0) return KL_ERR_SETUP;
+    dim3 grid(min(tiles_m * tiles_n, sms), 1, 1);
     return launch<256, 4, false>(ma, mb, args, grid, stream);
 }
 

@@ -10,7 +10,8 @@
 //     a_rows[position] the row of A to read (-1: padding; null: the position itself).  This is a
 //     mixture of experts: the list holds (token, choice) pairs.
 //
-// Epilogues: plain, or a gated activation over weights that hold N gate rows followed by N up rows:
+// Epilogues: plain, or a gated activation over weights that hold N gate rows followed by N up rows (or,
+// `interleaved`, blocks of 64 gate rows each followed by the 64 up rows of the same outputs, N % 64 == 0):
 //     g = min(gate, limit), u = clamp(up, -limit, limit) (no clamp when limit <= 0),
 //     y = g * sigmoid(alpha * g) * (u + shift).
 // Arithmetic is 32-bit FMA for both dtypes; every output is one thread's sum in ascending k, so a row's
@@ -27,7 +28,7 @@ template <typename TI, typename TO, int BM, int EPI>
 __global__ void __launch_bounds__(GG_THREADS)
 grouped_gemm_kernel(const TI* __restrict__ A, long long lda, long long a_gs, const int* __restrict__ a_rows,
                     const TI* __restrict__ W, long long w_gs, TO* __restrict__ C, long long ldc, long long c_gs,
-                    const int* __restrict__ tile_group, int M, int N, int K, float limit, float alpha, float shift) {
+                    const int* __restrict__ tile_group, int M, int N, int K, float limit, float alpha, float shift, int interleaved) {
     pdl_launch_dependents();
     pdl_wait();
     constexpr int RM = BM / 16;                                   // rows per thread
@@ -64,8 +65,11 @@ grouped_gemm_kernel(const TI* __restrict__ A, long long lda, long long a_gs, con
             const int e = threadIdx.x + r * GG_THREADS;
             const int row = e / GG_BK, kk = e % GG_BK, gn = n0 + row, gk = k0 + kk;
             const bool ok = gn < N && gk < K;
-            Ws[0][kk][row] = ok ? to_f32(Wg[(size_t)gn * K + gk]) : 0.f;
-            if (EPI == GG_GATED) Ws[1][kk][row] = ok ? to_f32(Wg[(size_t)(N + gn) * K + gk]) : 0.f;
+            // gate rows then up rows, or (interleaved) 64 gate rows, the 64 up rows of the same outputs, and so on
+            const size_t gate_row = (EPI == GG_GATED && interleaved) ? (size_t)(gn / 64) * 128 + gn % 64 : (size_t)gn;
+            const size_t up_row = interleaved ? gate_row + 64 : (size_t)N + gn;
+            Ws[0][kk][row] = ok ? to_f32(Wg[gate_row * K + gk]) : 0.f;
+            if (EPI == GG_GATED) Ws[1][kk][row] = ok ? to_f32(Wg[up_row * K + gk]) : 0.f;
         }
         __syncthreads();
 #pragma unroll
@@ -107,18 +111,138 @@ grouped_gemm_kernel(const TI* __restrict__ A, long long lda, long long a_gs, con
     }
 }
 
+// Few rows per group (a decode step's experts): the product is bound by reading each group's weights once.
+// A warp takes four weight rows (four outputs, or two outputs' gate and up rows), every lane 16 bytes of each
+// row per step, and multiplies them with up to GV_ROWS list places of the tile at once (their rows of A come
+// from L1 after the first touch); shuffles add the lanes.  bfloat16 operands, 32-bit sums, K % 8 == 0.
+constexpr int GV_ROWS = 8, GV_WARPS = 8;
+
+__device__ __forceinline__ void bf16x8_to_float(const uint4& raw, float (&f)[8]) {
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 v = __bfloat1622float2(p[j]);
+        f[2 * j] = v.x;
+        f[2 * j + 1] = v.y;
+    }
+}
+
+template <typename TO, bool GATED>
+__global__ void __launch_bounds__(GV_WARPS * 32)
+grouped_gemv_kernel(const bf16* __restrict__ A, long long lda, const int* __restrict__ a_rows, const int* __restrict__ live_rows,
+                    const bf16* __restrict__ W, long long w_gs,
+                    TO* __restrict__ C, long long ldc, const int* __restrict__ tile_group, int tile_rows, int N, int K,
+                    float limit, float alpha, float shift, int interleaved) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int g = tile_group[blockIdx.y];
+    if (g < 0) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int OUTS = GATED ? 2 : 4;                           // outputs per warp
+    const int n0 = (blockIdx.x * GV_WARPS + warp) * OUTS;
+    if (n0 >= N) return;
+    const bf16* Wg = W + (size_t)g * w_gs;
+    const bf16* wrow[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        int n = min(n0 + (GATED ? c / 2 : c), N - 1);
+        size_t row = n;
+        if (GATED) {
+            const size_t gate_row = interleaved ? (size_t)(n / 64) * 128 + n % 64 : (size_t)n;
+            row = (c & 1) ? (interleaved ? gate_row + 64 : (size_t)N + n) : gate_row;
+        }
+        wrow[c] = Wg + row * K;
+    }
+    const int m0 = blockIdx.y * tile_rows;
+    for (int r0 = 0; r0 < tile_rows; r0 += GV_ROWS) {
+        int src[GV_ROWS];
+        bool any = false;
+#pragma unroll
+        for (int r = 0; r < GV_ROWS; ++r) {
+            const int place = m0 + r0 + r;
+            src[r] = -1;
+            if (r0 + r < tile_rows) src[r] = a_rows ? a_rows[place] : (live_rows == nullptr || live_rows[place] >= 0 ? place : -1);
+            any = any || src[r] >= 0;
+        }
+        if (!any) continue;
+        float acc[GV_ROWS][4];
+#pragma unroll
+        for (int r = 0; r < GV_ROWS; ++r)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[r][c] = 0.f;
+        for (int k = lane * 8; k < K; k += 256) {
+            float w[4][8];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) bf16x8_to_float(*reinterpret_cast<const uint4*>(wrow[c] + k), w[c]);
+#pragma unroll
+            for (int r = 0; r < GV_ROWS; ++r) {
+                if (src[r] < 0) continue;
+                float x[8];
+                bf16x8_to_float(*reinterpret_cast<const uint4*>(A + (size_t)src[r] * lda + k), x);
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[r][c] = fmaf(x[j], w[c][j], acc[r][c]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < GV_ROWS; ++r) {
+            if (src[r] < 0) continue;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[r][c] = warp_sum(acc[r][c]);
+            if (lane != 0) continue;
+            TO* crow = C + (size_t)(m0 + r0 + r) * ldc;
+            if (GATED) {
+#pragma unroll
+                for (int o = 0; o < 2; ++o) {
+                    if (n0 + o >= N) continue;
+                    float gt = acc[r][2 * o], up = acc[r][2 * o + 1];
+                    if (limit > 0.f) { gt = fminf(gt, limit); up = fminf(fmaxf(up, -limit), limit); }
+                    crow[n0 + o] = from_f32<TO>(gt / (1.0f + expf(-alpha * gt)) * (up + shift));
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    if (n0 + c < N) crow[n0 + c] = from_f32<TO>(acc[r][c]);
+            }
+        }
+    }
+}
+
 }  // namespace kl
 
 using namespace kl;
+
+// The routed product for few rows per group (see grouped_gemv_kernel): bfloat16 operands with 16-byte aligned rows.
+// a_rows: the row of A every list place reads (-1: padding); or null: the place itself, where live_rows (if given) is not negative.
+KL_API int kl_grouped_gemv(const void* A, long long lda, const int* a_rows, const int* live_rows, const void* W, long long w_gs, void* C, long long ldc,
+                           const int* tile_group, int tiles, int tile_rows, int N, int K, int gated, float limit, float alpha,
+                           float shift, int interleaved, int out_dtype, cudaStream_t stream) {
+    if (tiles <= 0 || N <= 0) return KL_OK;
+    if (K <= 0 || K % 8 || lda % 8 || tile_rows <= 0 || tile_group == nullptr || (interleaved && (!gated || N % 64))) return KL_ERR_BAD_SIZE;
+    if ((((uintptr_t)A | (uintptr_t)W) & 15) != 0) return KL_ERR_BAD_ALIGN;
+    if (tiles > 65535) return KL_ERR_BAD_SIZE;
+    const int per_cta = GV_WARPS * (gated ? 2 : 4);
+    const dim3 grid((N + per_cta - 1) / per_cta, tiles);
+#define KL_GV(TO, G)                                                                                                      \
+    launch_kernel(grouped_gemv_kernel<TO, G>, grid, GV_WARPS * 32, 0, stream, (const bf16*)A, lda, a_rows, live_rows, (const bf16*)W, w_gs, \
+                  (TO*)C, ldc, tile_group, tile_rows, N, K, limit, alpha, shift, interleaved)
+    if (out_dtype == KL_BF16) { if (gated) KL_GV(bf16, true); else KL_GV(bf16, false); }
+    else if (out_dtype == KL_F32) { if (gated) KL_GV(float, true); else KL_GV(float, false); }
+    else return KL_ERR_BAD_DTYPE;
+#undef KL_GV
+    KL_LAUNCH_CHECK();
+    return KL_OK;
+}
 
 // groups: the number of groups of a batched call (ignored for a routed one, whose tile_group has
 // `tiles` entries).  gated: 0 plain (W_g is [N, K]), 1 gated activation (W_g is [2 N, K]).
 KL_API int kl_grouped_gemm(const void* A, long long lda, long long a_gs, const int* a_rows, const void* W, long long w_gs,
                            void* C, long long ldc, long long c_gs, const int* tile_group, int tiles, int tile_rows, int groups,
-                           int M, int N, int K, int gated, float limit, float alpha, float shift, int in_dtype, int out_dtype,
+                           int M, int N, int K, int gated, float limit, float alpha, float shift, int interleaved, int in_dtype, int out_dtype,
                            cudaStream_t stream) {
     if (M <= 0 || N <= 0) return KL_OK;
-    if (K <= 0 || (tile_rows != 16 && tile_rows != 64)) return KL_ERR_BAD_SIZE;
+    if (K <= 0 || (tile_rows != 16 && tile_rows != 64) || (interleaved && (!gated || N % 64))) return KL_ERR_BAD_SIZE;
     const int my = tile_group ? tiles : (M + tile_rows - 1) / tile_rows;
     const int gz = tile_group ? 1 : groups;
     if (my <= 0 || gz <= 0) return KL_OK;
@@ -126,7 +250,7 @@ KL_API int kl_grouped_gemm(const void* A, long long lda, long long a_gs, const i
     const dim3 grid((N + GG_BN - 1) / GG_BN, my, gz);
 #define KL_GG(TI, TO, BM, EPI)                                                                                              \
     launch_kernel(grouped_gemm_kernel<TI, TO, BM, EPI>, grid, GG_THREADS, 0, stream, (const TI*)A, lda, a_gs, a_rows,         \
-                  (const TI*)W, w_gs, (TO*)C, ldc, c_gs, tile_group, M, N, K, limit, alpha, shift)
+                  (const TI*)W, w_gs, (TO*)C, ldc, c_gs, tile_group, M, N, K, limit, alpha, shift, interleaved)
 #define KL_GG_BY(TI, TO)                                                                                                    \
     do {                                                                                                                    \
         if (tile_rows == 16) { if (gated) KL_GG(TI, TO, 16, GG_GATED); else KL_GG(TI, TO, 16, GG_PLAIN); }                  \

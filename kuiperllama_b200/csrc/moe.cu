@@ -134,9 +134,38 @@ moe_combine_kernel(const T* __restrict__ results, long long ld, const int* __res
     }
 }
 
+// rows[p] = x[list_rows[p]] for every place of the list, zeros at padding places: the operand of a product
+// whose loader reads whole tiles of consecutive rows.
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_gather_kernel(const T* __restrict__ x, long long ld, const int* __restrict__ list_rows, int cap, int width, T* __restrict__ rows) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int per = width / 8;                                  // 16-byte pieces per row
+    const size_t total = (size_t)cap * per;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t p = idx / per;
+        const int c = (int)(idx - p * per) * 8;
+        const int src = list_rows[p];
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (src >= 0) v = *reinterpret_cast<const uint4*>(x + (size_t)src * ld + c);
+        *reinterpret_cast<uint4*>(rows + p * width + c) = v;
+    }
+}
+
 }  // namespace kl
 
 using namespace kl;
+
+// bfloat16 rows of width % 8 == 0 on 16-byte boundaries.
+KL_API int kl_moe_gather(const void* x, long long ld, const int* list_rows, int cap, int width, void* rows, cudaStream_t stream) {
+    if (cap <= 0) return KL_OK;
+    if (width <= 0 || width % 8 || ld % 8 || (((uintptr_t)x | (uintptr_t)rows) & 15)) return KL_ERR_BAD_ALIGN;
+    const int blocks = kl::strided_grid((size_t)cap * (width / 8), 256, 16);
+    launch_kernel(moe_gather_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)x, ld, list_rows, cap, width, (bf16*)rows);
+    KL_LAUNCH_CHECK();
+    return KL_OK;
+}
 
 KL_API int kl_moe_route(const float* logits, long long ld, int tokens, int experts, int top, int renormalise, int* choice,
                         float* weight, cudaStream_t stream) {

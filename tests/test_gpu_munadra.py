@@ -125,6 +125,99 @@ def test_grouped_product_batched_and_routed(dtype):
                 assert torch.allclose(out[pp[p]].cpu().double(), full, atol=tol, rtol=tol), (tile, gated, p)
 
 
+def test_grouped_product_on_the_tensor_cores():
+    """The routed product in tiles of 128 places on the tensor cores (bfloat16): experts with no rows, with a few, with
+    more than a tile; plain and with the gated activation in the epilogue over interleaved gate and up rows."""
+    from kuiperllama_b200.csrc import ops
+    dev = "cuda:0"
+    g = torch.Generator().manual_seed(6)
+    E, K, ff, n, top = 6, 192, 128, 330, 2
+    x = torch.randn(n, K, generator=g).bfloat16()
+    choice = torch.randint(0, E - 1, (n, top), generator=g).int()
+    choice[:, 1] = (choice[:, 0] + 1 + choice[:, 1] % (E - 2)) % (E - 1)      # two different experts, expert E - 1 gets nobody
+    choice[:3, 0] = 0
+    gate, up = (torch.randn(E, ff, K, generator=g) / 8).bfloat16(), (torch.randn(E, ff, K, generator=g) / 8).bfloat16()
+    down = (torch.randn(E, 72, ff, generator=g) / 8).bfloat16()
+    wgu = torch.stack([ops.interleave_gate_up(gate[e], up[e]) for e in range(E)]).to(dev)
+    pair_pos, list_rows, tile_group = ops.moe_plan(choice.to(dev), E, 128)
+    rows = ops.moe_gather(x.to(dev), list_rows)
+    lr = list_rows.cpu()
+    assert torch.equal(rows.cpu()[lr >= 0], x[lr[lr >= 0].long()]) and float(rows.cpu()[lr < 0].abs().max()) == 0.0
+    for gated in ((0.8, 1.702, 1.0), (0.0, 1.0, 0.0)):
+        act = torch.full((lr.numel(), ff), 7.0, dtype=torch.bfloat16, device=dev)
+        ops.gemm_tcgen05_grouped(rows, wgu, act, tile_group, gated=gated)
+        res = torch.empty((lr.numel(), 72), dtype=torch.bfloat16, device=dev)
+        ops.gemm_tcgen05_grouped(act, down.to(dev), res, tile_group)
+        ops.check_status(torch.device(dev))
+        pp = pair_pos.cpu()
+        for p in range(0, n * top, 13):
+            e, xr = int(choice.reshape(-1)[p]), x[p // top].double()
+            gt, u = gate[e].double() @ xr, up[e].double() @ xr
+            if gated[0] > 0:
+                gt, u = gt.clamp(max=gated[0]), u.clamp(-gated[0], gated[0])
+            y = gt * torch.sigmoid(gated[1] * gt) * (u + gated[2])
+            assert torch.allclose(act[pp[p]].cpu().double(), y, atol=2e-2, rtol=2e-2), (gated, p)
+            assert torch.allclose(res[pp[p]].cpu().double(), down[e].double() @ act[pp[p]].cpu().double(), atol=2e-2, rtol=2e-2), (gated, p)
+
+
+def test_grouped_product_for_few_rows():
+    """The routed product's form for a decode step (a warp per four weight rows), against the tiled form: bfloat16."""
+    from kuiperllama_b200.csrc import ops
+    dev = "cuda:0"
+    g = torch.Generator().manual_seed(16)
+    E, K, ff, n, top = 7, 200, 128, 9, 3
+    x = torch.randn(n, K, generator=g).bfloat16().to(dev)
+    choice = torch.stack([torch.randperm(E - 1, generator=g)[:top] for _ in range(n)]).int()
+    gate, up = (torch.randn(E, ff, K, generator=g) / 8).bfloat16(), (torch.randn(E, ff, K, generator=g) / 8).bfloat16()
+    down = (torch.randn(E, 70, ff, generator=g) / 8).bfloat16().to(dev)
+    pair_pos, list_rows, tile_group = ops.moe_plan(choice.to(dev), E, 16)
+    cap = list_rows.numel()
+    for inter in (False, True):
+        w = torch.stack([ops.interleave_gate_up(gate[e], up[e]) if inter else torch.cat([gate[e], up[e]]) for e in range(E)]).to(dev)
+        for gated in ((0.8, 1.702, 1.0), (0.0, 1.0, 0.0)):
+            want, got = (torch.zeros(cap, ff, dtype=torch.bfloat16, device=dev) for _ in range(2))
+            ops.grouped_gemm(x, w, want, a_rows=list_rows, tile_group=tile_group, tile_rows=16, gated=gated, interleaved=inter)
+            ops.grouped_gemv(x, w, got, list_rows, tile_group, 16, gated=gated, interleaved=inter)
+            assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2) and float(want.abs().max()) > 0.1
+            want2, got2 = (torch.zeros(cap, 70, dtype=torch.bfloat16, device=dev) for _ in range(2))
+            ops.grouped_gemm(want, down, want2, tile_group=tile_group, tile_rows=16)
+            ops.grouped_gemv(want, down, got2, None, tile_group, 16, live_rows=list_rows)
+            live = (list_rows >= 0)
+            assert torch.allclose(got2.float()[live], want2.float()[live], atol=2e-2, rtol=2e-2)
+            assert float(got2.float()[~live].abs().max()) == 0.0, "padding places are left alone"
+
+
+@pytest.mark.parametrize("H, Dk, Dv", [(6, 96, 64), (32, 288, 256), (80, 48, 16), (3, 160, 144)])
+def test_latent_attention_on_the_tensor_cores(H, Dk, Dv):
+    """The tensor-core kernel for many heads over one key head against the plain kernel (bfloat16): prompts of unequal lengths
+    on scattered pages, portions that start inside a page, single tokens; with sinks."""
+    from kuiperllama_b200.csrc import ops
+    from kuiperllama_b200.parts.base import StepContext
+    dev = "cuda:0"
+    g = torch.Generator().manual_seed(H)
+    cache = (torch.randn(12, 1, 64, Dk, generator=g)).bfloat16().to(dev)
+    table = torch.tensor([[5, 2, 9, 0], [1, 7, 3, 11], [4, 6, 8, 10]], dtype=torch.int32, device=dev)
+    sink = torch.randn(H, generator=g).to(dev) * 2
+    for starts, news in (([0, 0, 0], [130, 1, 67]), ([100, 63, 200], [30, 2, 1]), ([150, 64, 255], [1, 1, 1])):
+        n = sum(news)
+        q = (torch.randn(n, H * Dk, generator=g) / 4).bfloat16().to(dev)
+        cu = [0]
+        for k in news:
+            cu.append(cu[-1] + k)
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+        pos = i32([st + i for st, k in zip(starts, news) for i in range(k)])
+        tslot = i32([sl for sl, k in enumerate(news) for _ in range(k)])
+        step = StepContext(n_tokens=n, n_seqs=3, token_ids=pos, positions=pos, token_slot=tslot, seq_slots=i32([0, 1, 2]), seq_starts=i32(starts),
+                           seq_new=i32(news), cu_tokens=i32(cu), is_decode=max(news) == 1, max_new=max(news), max_context=max(a + b for a, b in zip(starts, news)),
+                           host_slots=[0, 1, 2], host_starts=starts, host_new=news)
+        for sk in (None, sink):
+            want = torch.empty(n, H * Dv, dtype=torch.bfloat16, device=dev)
+            got = torch.full_like(want, 9.0)
+            ops.attention_simt(q, H * Dk, want, cache, cache, table, pos, tslot, n, H, 1, Dk, 0.3, 0, value_dim=Dv, sink=sk)
+            ops.latent_attention(q, got, cache, table, step, H, Dk, Dv, 0.3, sk)
+            assert torch.allclose(got.float(), want.float(), atol=3e-2, rtol=3e-2), (starts, news, sk is not None)
+
+
 def test_router_softmax_top_and_weights():
     """Scores over all experts, the largest first, the lower index among equals, weights not renormalised (or renormalised)."""
     from kuiperllama_b200.csrc import ops
