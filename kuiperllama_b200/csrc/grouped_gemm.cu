@@ -170,19 +170,31 @@ grouped_gemv_kernel(const bf16* __restrict__ A, long long lda, const int* __rest
         for (int r = 0; r < GV_ROWS; ++r)
 #pragma unroll
             for (int c = 0; c < 4; ++c) acc[r][c] = 0.f;
-        for (int k = lane * 8; k < K; k += 256) {
-            float w[4][8];
+        // two steps of 256 columns at a time: eight 16-byte loads of weights in flight per lane
+        for (int k = lane * 8; k < K; k += 512) {
+            const bool second = k + 256 < K;
+            uint4 raw[2][4];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) bf16x8_to_float(*reinterpret_cast<const uint4*>(wrow[c] + k), w[c]);
+            for (int c = 0; c < 4; ++c) {
+                raw[0][c] = *reinterpret_cast<const uint4*>(wrow[c] + k);
+                raw[1][c] = second ? *reinterpret_cast<const uint4*>(wrow[c] + k + 256) : make_uint4(0u, 0u, 0u, 0u);
+            }
 #pragma unroll
-            for (int r = 0; r < GV_ROWS; ++r) {
-                if (src[r] < 0) continue;
-                float x[8];
-                bf16x8_to_float(*reinterpret_cast<const uint4*>(A + (size_t)src[r] * lda + k), x);
+            for (int h = 0; h < 2; ++h) {
+                if (h == 1 && !second) break;
+                float w[4][8];
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
+                for (int c = 0; c < 4; ++c) bf16x8_to_float(raw[h][c], w[c]);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) acc[r][c] = fmaf(x[j], w[c][j], acc[r][c]);
+                for (int r = 0; r < GV_ROWS; ++r) {
+                    if (src[r] < 0) continue;
+                    float x[8];
+                    bf16x8_to_float(*reinterpret_cast<const uint4*>(A + (size_t)src[r] * lda + k + 256 * h), x);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) acc[r][c] = fmaf(x[j], w[c][j], acc[r][c]);
+                }
             }
         }
 #pragma unroll

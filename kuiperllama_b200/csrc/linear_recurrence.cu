@@ -10,7 +10,8 @@
 //                         1 - a^2 = -expm1(2 log a).  a and b overwrite the pre-activations.
 //   linear_scan_kernel    a thread per (sequence, channel) walks the step's tokens from the slot's state,
 //                         writes out[t, c] = S_t * gelu_tanh(y[t, c] + bias) in the compute dtype, leaves
-//                         the state updated and moves the convolution's inputs on.
+//                         the state updated and moves the convolution's inputs on.  Long prompts are cut into
+//                         chunks that run side by side (two passes and a carry between them).
 //
 // State of a slot: float32 [width] S, then [taps - 1][width] the convolution's last inputs, oldest first.
 // ExiledOfCode/KuiperLLama has no recurrent mixer (its mixer is mha_kernel.cu:61,74-106).
@@ -70,50 +71,90 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
     return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 
+// The convolution's inputs move on: the last taps - 1 inputs of the sequence, oldest first.
 template <typename T>
+__device__ __forceinline__ void move_taps(float* __restrict__ tail, const T* __restrict__ proj, long long ld, int x_col,
+                                          const float* __restrict__ x_bias, int taps, int row0, int n, int width, int c) {
+    if (taps <= 1) return;
+    const float xb = x_bias ? x_bias[c] : 0.f;
+    float keep[LR_MAX_TAPS];
+#pragma unroll
+    for (int q = 0; q < LR_MAX_TAPS; ++q) {
+        if (q < taps - 1) {
+            const int li = n - (taps - 1) + q;                     // the input that lands at place q
+            keep[q] = li >= 0 ? to_f32(proj[(size_t)(row0 + li) * ld + x_col + c]) + xb : tail[(size_t)(q + n) * width + c];
+        }
+    }
+#pragma unroll
+    for (int q = 0; q < LR_MAX_TAPS; ++q)
+        if (q < taps - 1) tail[(size_t)q * width + c] = keep[q];
+}
+
+// MODE 0: a thread walks all of its sequence's tokens from the slot's state and leaves the state updated.
+// Long prompts take three launches instead, over chunks of `chunk` tokens (blockIdx.y): MODE 1 leaves every chunk's
+// (product of a, result from zero) in scratch [sequences][chunks][2][width]; linear_carry_kernel walks the chunks,
+// puts every chunk's starting state where its product was and updates the slot's state; MODE 2 walks every chunk
+// again from its starting state and writes the outputs.
+template <typename T, int MODE>
 __global__ void __launch_bounds__(128)
 linear_scan_kernel(const float* __restrict__ gates, int block, const T* __restrict__ proj, long long ld, int y_col, int x_col,
                    const float* __restrict__ y_bias, const float* __restrict__ x_bias, int taps, float* __restrict__ state,
                    long long state_ld, const int* __restrict__ cu_tokens, const int* __restrict__ seq_slots,
-                   const int* __restrict__ seq_new, int width, T* __restrict__ out) {
+                   const int* __restrict__ seq_new, int width, T* __restrict__ out, float* __restrict__ scratch, int chunk) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int s = blockIdx.z;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int slot = seq_slots[s];
+    if (c >= width || slot < 0) return;
+    const int row0 = cu_tokens[s], n = seq_new[s];
+    const int l0 = MODE == 0 ? 0 : blockIdx.y * chunk, l1 = MODE == 0 ? n : min(n, l0 + chunk);
+    if (l0 >= n) return;
+    const int b = c / block, j = c - b * block;
+    float* st = state + (size_t)slot * state_ld;
+    float* sc = MODE == 0 ? nullptr : scratch + ((size_t)s * gridDim.y + blockIdx.y) * 2 * width;
+    float S = MODE == 0 ? st[c] : (MODE == 1 ? 0.f : sc[c]);
+    float P = 1.f;
+    const float yb = y_bias ? y_bias[c] : 0.f;
+    const float* g = gates + (size_t)row0 * 2 * width + (size_t)b * 2 * block + j;
+    const T* y = proj + (size_t)row0 * ld + y_col + c;
+    T* o = out + (size_t)row0 * width + c;
+#pragma unroll 4
+    for (int l = l0; l < l1; ++l) {
+        const float a = g[(size_t)l * 2 * width], bx = g[(size_t)l * 2 * width + block];
+        S = fmaf(a, S, bx);
+        if (MODE == 1) P *= a;
+        else o[(size_t)l * width] = from_f32<T>(S * gelu_tanh_f(to_f32(y[(size_t)l * ld]) + yb));
+    }
+    if (MODE == 1) { sc[c] = P; sc[width + c] = S; }
+    if (MODE == 0) {
+        st[c] = S;
+        move_taps(st + width, proj, ld, x_col, x_bias, taps, row0, n, width, c);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+linear_carry_kernel(float* __restrict__ scratch, int chunks, int chunk, const T* __restrict__ proj, long long ld, int x_col,
+                    const float* __restrict__ x_bias, int taps, float* __restrict__ state, long long state_ld,
+                    const int* __restrict__ cu_tokens, const int* __restrict__ seq_slots, const int* __restrict__ seq_new, int width) {
     pdl_launch_dependents();
     pdl_wait();
     const int s = blockIdx.y;
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     const int slot = seq_slots[s];
     if (c >= width || slot < 0) return;
-    const int row0 = cu_tokens[s], n = seq_new[s];
-    const int b = c / block, j = c - b * block;
+    const int n = seq_new[s];
     float* st = state + (size_t)slot * state_ld;
     float S = st[c];
-    const float yb = y_bias ? y_bias[c] : 0.f;
-    const float* g = gates + (size_t)row0 * 2 * width + (size_t)b * 2 * block + j;
-    const T* y = proj + (size_t)row0 * ld + y_col + c;
-    T* o = out + (size_t)row0 * width + c;
-#pragma unroll 4
-    for (int l = 0; l < n; ++l) {
-        const float a = g[(size_t)l * 2 * width], bx = g[(size_t)l * 2 * width + block];
-        const float yy = to_f32(y[(size_t)l * ld]);
-        S = fmaf(a, S, bx);
-        o[(size_t)l * width] = from_f32<T>(S * gelu_tanh_f(yy + yb));
+    for (int k = 0; k * chunk < n; ++k) {
+        float* sc = scratch + ((size_t)s * chunks + k) * 2 * width;
+        const float P = sc[c], B = sc[width + c];
+        sc[c] = S;
+        S = fmaf(P, S, B);
     }
     st[c] = S;
-    // the convolution's inputs move on: the last taps - 1 inputs of the sequence, oldest first
-    if (taps > 1) {
-        float* tail = st + width;
-        const float xb = x_bias ? x_bias[c] : 0.f;
-        float keep[LR_MAX_TAPS];
-#pragma unroll
-        for (int q = 0; q < LR_MAX_TAPS; ++q) {
-            if (q < taps - 1) {
-                const int li = n - (taps - 1) + q;                     // the input that lands at place q
-                keep[q] = li >= 0 ? to_f32(proj[(size_t)(row0 + li) * ld + x_col + c]) + xb : tail[(size_t)(q + n) * width + c];
-            }
-        }
-#pragma unroll
-        for (int q = 0; q < LR_MAX_TAPS; ++q)
-            if (q < taps - 1) tail[(size_t)q * width + c] = keep[q];
-    }
+    move_taps(st + width, proj, ld, x_col, x_bias, taps, cu_tokens[s], n, width, c);
 }
 
 }  // namespace kl
@@ -149,20 +190,34 @@ KL_API int kl_rglru_gate(float* gates, const float* u, const float* r_bias, cons
     return KL_OK;
 }
 
+// scratch: null (a thread per sequence and channel walks the whole step), or float32 [n_seqs][ceil(max_new / chunk)][2][width]
+// for the three launches over chunks of `chunk` tokens.
 KL_API int kl_linear_scan(const float* gates, int block, const void* proj, long long ld, int y_col, int x_col, const float* y_bias,
                           const float* x_bias, int taps, float* state, long long state_ld, const int* cu_tokens,
-                          const int* seq_slots, const int* seq_new, int n_seqs, int width, void* out, int dtype, cudaStream_t stream) {
+                          const int* seq_slots, const int* seq_new, int n_seqs, int max_new, int width, void* out, float* scratch,
+                          int chunk, int dtype, cudaStream_t stream) {
     if (n_seqs <= 0) return KL_OK;
     if (taps < 1 || taps > LR_MAX_TAPS || width <= 0 || block <= 0 || width % block || n_seqs > 65535) return KL_ERR_BAD_SIZE;
-    const dim3 grid((width + 127) / 128, n_seqs);
-    if (dtype == KL_F32)
-        launch_kernel(linear_scan_kernel<float>, grid, 128, 0, stream, gates, block, (const float*)proj, ld, y_col, x_col, y_bias, x_bias,
-                      taps, state, state_ld, cu_tokens, seq_slots, seq_new, width, (float*)out);
-    else if (dtype == KL_BF16)
-        launch_kernel(linear_scan_kernel<bf16>, grid, 128, 0, stream, gates, block, (const bf16*)proj, ld, y_col, x_col, y_bias, x_bias,
-                      taps, state, state_ld, cu_tokens, seq_slots, seq_new, width, (bf16*)out);
-    else
-        return KL_ERR_BAD_DTYPE;
+    if (dtype != KL_F32 && dtype != KL_BF16) return KL_ERR_BAD_DTYPE;
+    if (scratch != nullptr && (chunk <= 0 || max_new <= 0)) return KL_ERR_BAD_SIZE;
+    const int chunks = scratch ? (max_new + chunk - 1) / chunk : 1;
+    if (chunks > 65535) return KL_ERR_BAD_SIZE;
+    const dim3 grid((width + 127) / 128, chunks, n_seqs);
+#define KL_SCAN(T, MODE)                                                                                                    \
+    launch_kernel(linear_scan_kernel<T, MODE>, grid, 128, 0, stream, gates, block, (const T*)proj, ld, y_col, x_col, y_bias, x_bias, \
+                  taps, state, state_ld, cu_tokens, seq_slots, seq_new, width, (T*)out, scratch, chunk)
+#define KL_CARRY(T)                                                                                                         \
+    launch_kernel(linear_carry_kernel<T>, dim3((width + 127) / 128, n_seqs), 128, 0, stream, scratch, chunks, chunk, (const T*)proj, ld, \
+                  x_col, x_bias, taps, state, state_ld, cu_tokens, seq_slots, seq_new, width)
+    if (scratch == nullptr) {
+        if (dtype == KL_F32) KL_SCAN(float, 0); else KL_SCAN(bf16, 0);
+    } else if (dtype == KL_F32) {
+        KL_SCAN(float, 1); KL_LAUNCH_CHECK(); KL_CARRY(float); KL_LAUNCH_CHECK(); KL_SCAN(float, 2);
+    } else {
+        KL_SCAN(bf16, 1); KL_LAUNCH_CHECK(); KL_CARRY(bf16); KL_LAUNCH_CHECK(); KL_SCAN(bf16, 2);
+    }
+#undef KL_SCAN
+#undef KL_CARRY
     KL_LAUNCH_CHECK();
     return KL_OK;
 }

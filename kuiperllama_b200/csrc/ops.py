@@ -586,6 +586,10 @@ def latent_attention(qfull: torch.Tensor, out: torch.Tensor, cache: torch.Tensor
 
 # --------------------------------------------------------------------------- gated linear recurrence
 
+LINEAR_SCAN_CHUNK = 64           # tokens per chunk of the chunked scan
+LINEAR_SCAN_CHUNKED_FROM = 256   # tokens of the longest sequence from which a step takes it
+
+
 def causal_conv(proj: torch.Tensor, x_col: int, x_bias: Optional[torch.Tensor], weight: torch.Tensor, bias: Optional[torch.Tensor],
                 state: torch.Tensor, step, width: int, out: torch.Tensor) -> None:
     """out[t, c] (float32) = bias[c] + sum_k weight[c, k] * x[t - (taps - 1 - k), c], x = proj[:, x_col + c] + x_bias[c];
@@ -625,10 +629,17 @@ def linear_scan(gates: torch.Tensor, block: int, proj: torch.Tensor, y_col: int,
     _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1 and state.shape[1] >= width * taps, "linear_scan: state")
     _need(out.is_contiguous() and out.dtype == proj.dtype and out.shape[1] == width and out.shape[0] >= step.n_tokens, "linear_scan: out")
     _need(proj.stride(1) == 1 and max(y_col, x_col) + width <= proj.shape[1], "linear_scan: projections")
+    # A step with long sequences runs in chunks side by side (a chunk's decay product and result from zero; the states at the
+    # chunks' starts; the chunks again with their outputs); a thread that walks its channel alone is faster for few tokens.
+    scratch, launches = None, 1
+    if step.max_new >= LINEAR_SCAN_CHUNKED_FROM:
+        chunks = -(-step.max_new // LINEAR_SCAN_CHUNK)
+        scratch = torch.empty(step.n_seqs * chunks * 2 * width, dtype=torch.float32, device=proj.device)
+        launches = 3
     _check(lib("linear_recurrence").kl_linear_scan(
         _ptr(gates), block, _ptr(proj), ctypes.c_longlong(proj.stride(0)), y_col, x_col, _ptr(y_bias), _ptr(x_bias), taps, _ptr(state),
-        ctypes.c_longlong(state.stride(0)), _ptr(step.cu_tokens), _ptr(step.seq_slots), _ptr(step.seq_new), step.n_seqs, width,
-        _ptr(out), dtype_code(proj.dtype), _stream()), "linear_scan")
+        ctypes.c_longlong(state.stride(0)), _ptr(step.cu_tokens), _ptr(step.seq_slots), _ptr(step.seq_new), step.n_seqs, step.max_new,
+        width, _ptr(out), _ptr(scratch), LINEAR_SCAN_CHUNK, dtype_code(proj.dtype), _stream()), "linear_scan", launches)
 
 
 # --------------------------------------------------------------------------- matrix products

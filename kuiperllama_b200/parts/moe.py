@@ -30,7 +30,7 @@ class MoEFeedForward(FeedForward):
     ``names``: router and, with ``{e}`` for the expert's number, gate, up, down.  KuiperLLama's only feed-forward is
     the dense SwiGLU (kuiper/source/model/llama3.cpp:692-718)."""
 
-    TENSOR_CORE_ROWS_PER_EXPERT = 48     # mean rows per expert from which the list is cut into tiles of 128 for the tensor cores
+    TENSOR_CORE_ROWS_PER_EXPERT = int(__import__('os').environ.get('KL_MOE_TC_ROWS', '48'))     # mean rows per expert from which the list is cut into tiles of 128 for the tensor cores
 
     @classmethod
     def manifest(cls, spec: PartSpec, prefix: str) -> Dict[str, TensorDecl]:

@@ -280,6 +280,29 @@ def test_whole_prompt_portions_and_single_tokens(models, name, dtype):
         assert_logits(_run_in_steps(_engine(model), toks, cuts), ref, dtype, f"{name}: steps of {cuts[:6]}")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["mixed", "odd"])
+def test_long_prompts_take_the_chunked_scan(models, name, dtype):
+    """From 256 tokens of a sequence in one step the recurrence runs in chunks of 64 side by side: a long prompt, a long
+    portion after a short one and before one, and a long prompt beside a short one in one step."""
+    from kuiperllama_b200.csrc import ops
+    model, folder = models(name, dtype, seed=1)
+    V = CONFIGS[name]["vocab"]
+    toks = tokens(330, V, seed=41)
+    assert 330 >= ops.LINEAR_SCAN_CHUNKED_FROM and 330 % ops.LINEAR_SCAN_CHUNK
+    ref = oracle_logits(folder, toks)
+    for cuts in ([330], [300, 30], [31, 299]):
+        assert_logits(_run_in_steps(_engine(model), toks, cuts), ref, dtype, f"{name}: long steps of {cuts}")
+    short = tokens(70, V, seed=42)
+    eng = _engine(model)
+    with torch.inference_mode():
+        a, b = eng.alloc_slot(), eng.alloc_slot()
+        out = eng.step([_inputs(a, short), _inputs(b, toks)])
+    eng.check_device_errors()
+    assert_logits(out[:70], oracle_logits(folder, short), dtype, f"{name}: a short prompt beside a long one")
+    assert_logits(out[70:], ref, dtype, f"{name}: a long prompt beside a short one")
+
+
 @pytest.mark.parametrize("use_graphs", [False, True])
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", FULL)
