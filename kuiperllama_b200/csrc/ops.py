@@ -391,7 +391,8 @@ def attention_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: t
 
 def grouped_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, a_group_stride: int = 0, out_group_stride: int = 0,
                  rows: Optional[int] = None, a_rows: Optional[torch.Tensor] = None, tile_group: Optional[torch.Tensor] = None,
-                 tile_rows: int = 64, gated: Optional[tuple] = None, interleaved: bool = False) -> None:
+                 tile_rows: int = 64, gated: Optional[tuple] = None, interleaved: bool = False,
+                 row_gate: Optional[torch.Tensor] = None) -> None:
     """out_g = a_g @ w[g]^T for every group g, with ``w`` [groups, N (2 N if gated), K].
 
     Batched (``tile_group`` None): all ``rows`` rows for every group; group g reads the columns of ``a`` from
@@ -400,7 +401,8 @@ def grouped_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, a_group
     tile_rows] the row of ``a`` each place reads (-1: padding; None: the place itself); ``out`` is indexed by
     place.  ``gated`` = (limit, alpha, shift): the weights hold N gate rows then N up rows and the result
     is min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u, -limit, limit) + shift); limit <= 0 clamps nothing.
-    ``interleaved``: the gated weights alternate 64 gate rows and the 64 up rows of the same outputs instead."""
+    ``interleaved``: the gated weights alternate 64 gate rows and the 64 up rows of the same outputs instead.
+    ``row_gate`` [rows, groups] (batched, plain): group g's result of row t is multiplied by sigmoid(row_gate[t, g])."""
     _cuda(a, w, out, a_rows, tile_group)
     _i32(a_rows, "a_rows"); _i32(tile_group, "tile_group")
     _need(w.dim() == 3 and w.is_contiguous() and a.dtype == w.dtype, "grouped_gemm: weights must be contiguous [groups, N, K] in a's dtype")
@@ -423,10 +425,15 @@ def grouped_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, a_group
         _need(a_rows is not None or a.shape[0] >= M, "grouped_gemm: a holds fewer rows than the list")
         a_group_stride = out_group_stride = 0
     lim, alpha, shift = gated if gated is not None else (0.0, 1.0, 0.0)
+    if row_gate is not None:
+        _cuda(row_gate)
+        _need(tile_group is None and gated is None and row_gate.dtype == a.dtype and row_gate.dim() == 2 and row_gate.stride(1) == 1
+              and row_gate.shape[0] >= M and row_gate.shape[1] == G, "grouped_gemm: row_gate is [rows, groups] of a batched plain product")
     _check(lib("grouped_gemm").kl_grouped_gemm(
         _ptr(a), ctypes.c_longlong(a.stride(0)), ctypes.c_longlong(a_group_stride), _ptr(a_rows), _ptr(w), ctypes.c_longlong(NW * K),
         _ptr(out), ctypes.c_longlong(out.stride(0)), ctypes.c_longlong(out_group_stride), _ptr(tile_group), tiles, tile_rows, G, M, N, K,
-        int(gated is not None), ctypes.c_float(lim), ctypes.c_float(alpha), ctypes.c_float(shift), int(bool(interleaved)), dtype_code(a.dtype),
+        int(gated is not None), ctypes.c_float(lim), ctypes.c_float(alpha), ctypes.c_float(shift), int(bool(interleaved)), _ptr(row_gate),
+        ctypes.c_longlong(0 if row_gate is None else row_gate.stride(0)), dtype_code(a.dtype),
         dtype_code(out.dtype), _stream()), "grouped_gemm")
 
 

@@ -106,7 +106,7 @@ class LatentAttentionMixer(Mixer):
         lat = make((n, self.H * self.r), dtype=dt, device=dev)
         ops.latent_attention(qfull, lat, cache.k, cache.block_table, step, self.H, self.Dk, self.r, self.scale, self.sink)
         attn = torch.empty((n, self.H * self.dv), dtype=dt, device=dev)
-        ops.grouped_gemm(lat, self.uv, attn, a_group_stride=self.r, out_group_stride=self.dv, rows=n, tile_rows=16 if n <= 16 else 64)
-        if self.gated:
-            ops.sigmoid_gate(attn, self.inputs.view("g"), group=self.dv)
+        # W_uv per head, and each head's result times sigmoid of its gate number in the same kernel
+        ops.grouped_gemm(lat, self.uv, attn, a_group_stride=self.r, out_group_stride=self.dv, rows=n, tile_rows=16 if n <= 16 else 64,
+                         row_gate=self.inputs.view("g") if self.gated else None)
         return self.o.forward(attn, allow_partials=True)

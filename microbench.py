@@ -11,7 +11,7 @@ repeats, a buffer larger than L2 written between repeats), and print the achieve
         fixes the number of pieces the decode attention cuts a sequence into, else the package's rule)
     python microbench.py prefill_step --shape 8b --layers 2 --tokens 2048
         (one prompt through a few layers, launched kernel by kernel: the case for a launch list)
-    python microbench.py prefill_step --design terolix --shape 1b --layers 4 --tokens 2048     (the other architecture)
+    python microbench.py prefill_step --design terolix --shape 1b --layers 4 --tokens 2048     (another architecture; also munadra)
 
 It is also the small case that profiler captures of single kernels are taken on.
 """
@@ -68,6 +68,11 @@ def _model_config(args, positions: int) -> dict:
         if z is None:
             raise SystemExit("--design terolix has the shapes 1b and 8b")
         return bench.terolix_config(z["width"], args.layers, z["heads"], z["kv_heads"], z["head_dim"], z["ff"], 32000)
+    if args.design == "munadra":
+        z = {"1b": bench.COMPARE_SIZES["1b"], "8b": bench.COMPARE_SIZES["8b-8-layers"]}.get(args.shape)
+        if z is None:
+            raise SystemExit("--design munadra has the shapes 1b and 8b")
+        return bench.munadra_config(z["width"], args.layers, z["heads"], z["head_dim"], 32000)
     base = {"8b": bench.LLAMA31_8B, "7b": bench.LLAMA2_7B, "1b": bench.LLAMA32_1B, "70b": bench.LLAMA3_70B}[args.shape]
     return dict(base, num_hidden_layers=args.layers, max_position_embeddings=max(base["max_position_embeddings"], positions))
 
@@ -147,7 +152,7 @@ def main(argv=None) -> int:
     ap.add_argument("kernel", choices=["gemm_skinny", "gemm_tcgen05", "attention_prefill", "attention_decode", "decode_step",
                                            "prefill_step"])
     ap.add_argument("--shape", default="8b", choices=["8b", "7b", "1b", "70b"], help="decode_step: which of bench.py's shapes")
-    ap.add_argument("--design", default="llama", choices=["llama", "terolix"],
+    ap.add_argument("--design", default="llama", choices=["llama", "terolix", "munadra"],
                     help="decode_step, prefill_step: the Llama shape, or the Terolix model of that width (1b, 8b; layers in the order "
                          "minGRU, minGRU, attention, delta rule)")
     ap.add_argument("--layers", type=int, default=4, help="decode_step: layers of the model")

@@ -103,6 +103,10 @@ def test_grouped_product_batched_and_routed(dtype):
         want = torch.einsum("tgk,gnk->tgn", a.double().reshape(37, 5, 20)[..., :12], w.double())
         got = out.cpu().double().reshape(37, 5, 9)
         assert torch.allclose(got[..., :7], want, atol=tol, rtol=tol) and float(got[..., 7:].abs().max()) == 0.0
+        gate = rnd(37, 5).to(dt)                                           # one number per row and group on the result
+        ops.grouped_gemm(a.to(dev), w.to(dev), out, a_group_stride=20, out_group_stride=9, rows=37, tile_rows=tile, row_gate=gate.to(dev))
+        got = out.cpu().double().reshape(37, 5, 9)
+        assert torch.allclose(got[..., :7], want * torch.sigmoid(gate.double())[..., None], atol=tol, rtol=tol)
     # routed: 50 tokens choose 2 of 6 groups (one group gets nobody)
     x, wgu, choice = rnd(50, 24).to(dt), (rnd(6, 2 * 10, 24) / 4).to(dt), torch.randint(0, 5, (50, 2), generator=g).int()
     for tile in (16, 64):
