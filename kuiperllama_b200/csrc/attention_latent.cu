@@ -9,7 +9,8 @@
 // exp2), P as the A operand straight from the accumulators, O += P V with V = the same page's first Dv
 // columns read through ldmatrix.trans.  O stays in registers (16 x Dv per warp), so Dv <= 256 here; wider
 // latents and float32 take the plain kernel (attention_simt.cu).  A sink per head joins the denominator at
-// the end.  Rows of shared memory are Dk + 8 elements apart, which keeps the eight rows of an ldmatrix on
+// the end.  In a decode step a sequence's pages are cut over several CTAs (split-KV) whose pieces a small kernel
+// merges, so that few sequences still fill the machine.  Rows of shared memory are Dk + 8 elements apart, which keeps the eight rows of an ldmatrix on
 // different banks when Dk is a multiple of 16.
 //
 // Every row's sums run over the pages in ascending order whatever the step brings, so the result does not
@@ -55,7 +56,8 @@ __global__ void __launch_bounds__(LA_THREADS)
 latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const bf16* __restrict__ cache,
                             const int* __restrict__ block_table, int blocks_per_seq, const int* __restrict__ cu_tokens,
                             const int* __restrict__ seq_slots, const int* __restrict__ seq_starts, const int* __restrict__ seq_new,
-                            const float* __restrict__ sink, int H, int HB, int TT, int Dk, int Dv, float scale_log2) {
+                            const float* __restrict__ sink, int H, int HB, int TT, int Dk, int Dv, float scale_log2,
+                            int splits, float* __restrict__ part) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -63,7 +65,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, 
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                   // [64][ld]
     bf16* Ks = Qs + (size_t)LA_ROWS * ld;                           // [2][64][ld]
 
-    const int s = blockIdx.z, n_new = seq_new[s], t0 = blockIdx.x * TT, h0 = blockIdx.y * HB;
+    const int s = blockIdx.z, n_new = seq_new[s], t0 = blockIdx.x * TT, h0 = (blockIdx.y / splits) * HB, piece = blockIdx.y % splits;
     const int slot = seq_slots[s];
     if (t0 >= n_new || slot < 0) return;
     const int start = seq_starts[s], row0 = cu_tokens[s];
@@ -71,7 +73,10 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, 
     const int chunks = Dk / 8;                                      // 16-byte pieces per row
     const int* table = block_table + (size_t)slot * blocks_per_seq;
     const int tokens_here = min(TT, n_new - t0);
-    const int last_page = (start + t0 + tokens_here - 1) / PAGE;
+    // this CTA's pages: all of them, or (splits > 1, a decode step) one of `splits` runs of pages
+    const int all_pages = (start + t0 + tokens_here - 1) / PAGE + 1;
+    const int per = (all_pages + splits - 1) / splits;
+    const int first_page = piece * per, last_page = min(all_pages, first_page + per) - 1;
 
     auto load_page = [&](int j, int buf) {
         const bf16* src = cache + (size_t)table[j] * PAGE * Dk;
@@ -81,7 +86,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, 
             cp_async16(dst + (size_t)r * ld + c * 8, src + (size_t)r * Dk + c * 8);
         }
     };
-    load_page(0, 0);
+    if (first_page <= last_page) load_page(first_page, 0);
     cp_async_commit();
     // the query rows: row r is token t0 + r / HB, head h0 + r % HB; rows beyond the tile's tokens or heads are zeros
     for (int e = threadIdx.x; e < LA_ROWS * chunks; e += LA_THREADS) {
@@ -110,8 +115,8 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, 
         for (int c = 0; c < 4; ++c) o[n][c] = 0.f;
     const int nv = Dv / 8;                                          // value tiles in use (uniform)
 
-    for (int j = 0; j <= last_page; ++j) {
-        const int buf = j & 1;
+    for (int j = first_page; j <= last_page; ++j) {
+        const int buf = (j - first_page) & 1;
         if (j < last_page) load_page(j + 1, buf ^ 1);
         cp_async_commit();
         cp_async_wait<1>();
@@ -196,6 +201,15 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, 
         l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
         if (!live[i]) continue;
         const int r = warp * 16 + g + 8 * i, tt = r / HB, h = h0 + r % HB;
+        if (splits > 1) {
+            // a piece: the sums as they are (relative to this piece's maximum), the maximum and the sum of weights
+            float* pr = part + (((size_t)(row0 + t0 + tt) * H + h) * splits + piece) * (Dv + 2);
+#pragma unroll
+            for (int n = 0; n < NVT; ++n)
+                if (n < nv) *reinterpret_cast<float2*>(pr + n * 8 + 2 * quad) = make_float2(o[n][2 * i], o[n][2 * i + 1]);
+            if (quad == 0) { pr[Dv] = m[i]; pr[Dv + 1] = l[i]; }
+            continue;
+        }
         float w = 1.f, denom = l[i];
         if (sink != nullptr) {
             const float sk = sink[h] * 1.4426950408889634f;           // in the exp2 domain, as the scores are
@@ -211,20 +225,53 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, 
     }
 }
 
+// The pieces of a decode step's rows put together: a warp per (token, head); out = sum_p O_p 2^(m_p - M) / (sum_p l_p 2^(m_p - M) +
+// 2^(sink - M)), M the largest of the maxima and the sink, pieces in ascending order.
+__global__ void __launch_bounds__(128)
+latent_attention_merge_kernel(const float* __restrict__ part, int splits, const float* __restrict__ sink, int rows, int H, int Dv,
+                              bf16* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const float* pr = part + (size_t)row * splits * (Dv + 2);
+    const float sk = sink ? sink[row % H] * 1.4426950408889634f : -INFINITY;
+    // lane p holds piece p's maximum and sum of weights (splits <= 32), then its factor 2^(m_p - M)
+    const float mp = lane < splits ? pr[(size_t)lane * (Dv + 2) + Dv] : -INFINITY;
+    const float lp = lane < splits ? pr[(size_t)lane * (Dv + 2) + Dv + 1] : 0.f;
+    const float M = fmaxf(warp_max(mp), sk);
+    const float f = mp == -INFINITY ? 0.f : exp2f(mp - M);
+    const float denom = warp_sum(lp * f) + (sink ? exp2f(sk - M) : 0.f);
+    for (int d0 = 0; d0 < Dv; d0 += 32) {
+        const int d = d0 + lane;
+        float acc = 0.f;
+#pragma unroll 8
+        for (int p = 0; p < splits; ++p) {
+            const float fp = __shfl_sync(0xffffffffu, f, p);
+            if (d < Dv) acc = fmaf(pr[(size_t)p * (Dv + 2) + d], fp, acc);
+        }
+        if (d < Dv) out[(size_t)row * Dv + d] = __float2bfloat16_rn(acc / denom);
+    }
+}
+
 }  // namespace kl
 
 using namespace kl;
 
 // q: [tokens, H, Dk], out: [tokens, H, Dv], cache: [pages, 1, 64, Dk], all bfloat16; Dk % 16 == 0, Dv % 16 == 0, Dv <= 256
 // and <= Dk.  scale multiplies the dot products; sink: float32 [H] or null.  max_new: the most tokens a sequence brings.
+// splits > 1 (a decode step: one token per sequence): every sequence's pages are cut into that many runs, each a CTA that
+// leaves its sums in part (float32 [n_tokens * H][splits][Dv + 2]), and a second kernel puts the pieces together.
 KL_API int kl_latent_attention_mma(const void* q, void* out, const void* cache, const int* block_table, int blocks_per_seq,
                                    const int* cu_tokens, const int* seq_slots, const int* seq_starts, const int* seq_new, int n_seqs,
-                                   int max_new, const float* sink, int H, int Dk, int Dv, float scale, cudaStream_t stream) {
+                                   int max_new, const float* sink, int H, int Dk, int Dv, float scale, int splits, float* part,
+                                   int n_tokens, cudaStream_t stream) {
     if (n_seqs <= 0 || max_new <= 0) return KL_OK;
+    if (splits < 1 || splits > 32 || (splits > 1 && (part == nullptr || max_new != 1 || Dv % 2))) return KL_ERR_BAD_SIZE;
     if (H <= 0 || Dk % 16 || Dv % 16 || Dv <= 0 || Dv > 256 || Dv > Dk) return KL_ERR_BAD_SIZE;
     if ((((uintptr_t)q | (uintptr_t)out | (uintptr_t)cache) & 15) != 0) return KL_ERR_BAD_ALIGN;
     const int HB = H < LA_ROWS ? H : LA_ROWS, TT = LA_ROWS / HB;
-    const dim3 grid((max_new + TT - 1) / TT, (H + HB - 1) / HB, n_seqs);
+    const dim3 grid((max_new + TT - 1) / TT, ((H + HB - 1) / HB) * splits, n_seqs);
     if (grid.y > 65535 || grid.z > 65535) return KL_ERR_BAD_SIZE;
     const size_t smem = (size_t)3 * LA_ROWS * (Dk + 8) * sizeof(bf16);
     if (smem > 220 * 1024) return KL_ERR_BAD_SIZE;
@@ -238,7 +285,7 @@ KL_API int kl_latent_attention_mma(const void* q, void* out, const void* cache, 
         }                                                                                                                     \
         launch_kernel(latent_attention_mma_kernel<NVT>, grid, LA_THREADS, smem, stream, (const bf16*)q, (bf16*)out,           \
                       (const bf16*)cache, block_table, blocks_per_seq, cu_tokens, seq_slots, seq_starts, seq_new, sink, H, HB, TT, \
-                      Dk, Dv, scale_log2);                                                                                    \
+                      Dk, Dv, scale_log2, splits, part);                                                                      \
     } while (0)
     if (Dv <= 64) KL_LA(8);
     else if (Dv <= 128) KL_LA(16);
@@ -246,5 +293,10 @@ KL_API int kl_latent_attention_mma(const void* q, void* out, const void* cache, 
     else KL_LA(32);
 #undef KL_LA
     KL_LAUNCH_CHECK();
+    if (splits > 1) {
+        const int rows = n_tokens * H;
+        launch_kernel(latent_attention_merge_kernel, (rows + 3) / 4, 128, 0, stream, (const float*)part, splits, sink, rows, H, Dv, (bf16*)out);
+        KL_LAUNCH_CHECK();
+    }
     return KL_OK;
 }

@@ -115,6 +115,90 @@ grouped_gemm_kernel(const TI* __restrict__ A, long long lda, long long a_gs, con
     }
 }
 
+// The batched form on the tensor cores (bfloat16, mma.sync m16n8k16, 32-bit sums): per-head projections of a prompt's rows,
+// whose k and n are a head's sizes (tens to hundreds) and whose groups are the heads.  A CTA of four warps makes a tile of
+// 64 rows x 64 outputs of one group, 64 k at a time through shared memory (rows 72 elements apart: no bank conflicts for
+// ldmatrix); each warp 16 rows x 64 outputs.  Operands' rows and group offsets must lie on 16-byte boundaries.
+__device__ __forceinline__ void gg_ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void gg_mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+constexpr int GM_TILE = 64, GM_LD = 72;
+
+__global__ void __launch_bounds__(128)
+grouped_gemm_mma_kernel(const bf16* __restrict__ A, long long lda, long long a_gs, const bf16* __restrict__ W, long long w_gs,
+                        bf16* __restrict__ C, long long ldc, long long c_gs, int M, int N, int K,
+                        const bf16* __restrict__ row_gate, long long gate_ld) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ __align__(16) bf16 As[GM_TILE][GM_LD];
+    __shared__ __align__(16) bf16 Ws[GM_TILE][GM_LD];
+    const int g = blockIdx.z, m0 = blockIdx.y * GM_TILE, n0 = blockIdx.x * GM_TILE;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bf16* Ag = A + (size_t)g * a_gs;
+    const bf16* Wg = W + (size_t)g * w_gs;
+    float acc[8][4];
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[n][c] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += GM_TILE) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int e = threadIdx.x + i * 128, r = e >> 3, c = (e & 7) * 8;      // 64 rows x 8 pieces of 16 bytes
+            uint4 va = make_uint4(0u, 0u, 0u, 0u), vw = va;
+            if (k0 + c < K) {
+                if (m0 + r < M) va = *reinterpret_cast<const uint4*>(Ag + (size_t)(m0 + r) * lda + k0 + c);
+                if (n0 + r < N) vw = *reinterpret_cast<const uint4*>(Wg + (size_t)(n0 + r) * K + k0 + c);
+            }
+            *reinterpret_cast<uint4*>(&As[r][c]) = va;
+            *reinterpret_cast<uint4*>(&Ws[r][c]) = vw;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < GM_TILE; kk += 16) {
+            if (k0 + kk >= K) break;
+            uint32_t a[4];
+            gg_ldmatrix_x4(a, &As[warp * 16 + (lane & 15)][kk + (lane >> 4) * 8]);
+#pragma unroll
+            for (int n2 = 0; n2 < 4; ++n2) {
+                uint32_t b[4];
+                gg_ldmatrix_x4(b, &Ws[n2 * 16 + (lane & 7) + (lane >> 4) * 8][kk + ((lane >> 3) & 1) * 8]);
+                gg_mma_bf16(acc[2 * n2], a, b[0], b[1]);
+                gg_mma_bf16(acc[2 * n2 + 1], a, b[2], b[3]);
+            }
+        }
+        __syncthreads();
+    }
+    bf16* Cg = C + (size_t)g * c_gs;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int row = m0 + warp * 16 + (lane >> 2) + 8 * i;
+        if (row >= M) continue;
+        const float rg = row_gate ? 1.0f / (1.0f + expf(-to_f32(row_gate[(size_t)row * gate_ld + g]))) : 1.0f;
+        bf16* crow = Cg + (size_t)row * ldc;
+        const bool pairs = (((uintptr_t)Cg | (uintptr_t)(ldc * 2)) & 3) == 0;      // two neighbours as one 4-byte store
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+            const int col = n0 + n * 8 + 2 * (lane & 3);
+            if (pairs && col + 1 < N) {
+                const __nv_bfloat162 v = __floats2bfloat162_rn(acc[n][2 * i] * rg, acc[n][2 * i + 1] * rg);
+                *reinterpret_cast<__nv_bfloat162*>(crow + col) = v;
+            } else {
+                if (col < N) crow[col] = __float2bfloat16_rn(acc[n][2 * i] * rg);
+                if (col + 1 < N) crow[col + 1] = __float2bfloat16_rn(acc[n][2 * i + 1] * rg);
+            }
+        }
+    }
+}
+
 // Few rows per group (a decode step's experts): the product is bound by reading each group's weights once.
 // A warp takes four weight rows (four outputs, or two outputs' gate and up rows), every lane 16 bytes of each
 // row per step, and multiplies them with up to GV_ROWS list places of the tile at once (their rows of A come
@@ -229,6 +313,22 @@ grouped_gemv_kernel(const bf16* __restrict__ A, long long lda, const int* __rest
 }  // namespace kl
 
 using namespace kl;
+
+// The batched product on the tensor cores (see grouped_gemm_mma_kernel): bfloat16 in and out, K % 8 == 0, rows and group
+// offsets of A on 16-byte boundaries.
+KL_API int kl_grouped_gemm_mma(const void* A, long long lda, long long a_gs, const void* W, long long w_gs, void* C, long long ldc,
+                               long long c_gs, int groups, int M, int N, int K, const void* row_gate, long long gate_ld,
+                               cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || groups <= 0) return KL_OK;
+    if (K <= 0 || K % 8 || lda % 8 || a_gs % 8 || w_gs % 8) return KL_ERR_BAD_ALIGN;
+    if ((((uintptr_t)A | (uintptr_t)W) & 15) != 0) return KL_ERR_BAD_ALIGN;
+    const dim3 grid((N + GM_TILE - 1) / GM_TILE, (M + GM_TILE - 1) / GM_TILE, groups);
+    if (grid.y > 65535 || grid.z > 65535) return KL_ERR_BAD_SIZE;
+    launch_kernel(grouped_gemm_mma_kernel, grid, 128, 0, stream, (const bf16*)A, lda, a_gs, (const bf16*)W, w_gs, (bf16*)C, ldc, c_gs,
+                  M, N, K, (const bf16*)row_gate, gate_ld);
+    KL_LAUNCH_CHECK();
+    return KL_OK;
+}
 
 // The routed product for few rows per group (see grouped_gemv_kernel): bfloat16 operands with 16-byte aligned rows.
 // a_rows: the row of A every list place reads (-1: padding); or null: the place itself, where live_rows (if given) is not negative.

@@ -389,6 +389,9 @@ def attention_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: t
 
 # --------------------------------------------------------------------------- grouped products
 
+GROUPED_MMA_FROM_ROWS = 32       # rows from which a batched bfloat16 product takes the tensor-core kernel
+
+
 def grouped_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, a_group_stride: int = 0, out_group_stride: int = 0,
                  rows: Optional[int] = None, a_rows: Optional[torch.Tensor] = None, tile_group: Optional[torch.Tensor] = None,
                  tile_rows: int = 64, gated: Optional[tuple] = None, interleaved: bool = False,
@@ -429,6 +432,14 @@ def grouped_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, a_group
         _cuda(row_gate)
         _need(tile_group is None and gated is None and row_gate.dtype == a.dtype and row_gate.dim() == 2 and row_gate.stride(1) == 1
               and row_gate.shape[0] >= M and row_gate.shape[1] == G, "grouped_gemm: row_gate is [rows, groups] of a batched plain product")
+    if (tile_group is None and gated is None and a.dtype == out.dtype == torch.bfloat16 and M >= GROUPED_MMA_FROM_ROWS and K % 8 == 0
+            and a.stride(0) % 8 == 0 and a_group_stride % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
+        # a prompt's per-head projections: the tensor cores
+        _check(lib("grouped_gemm").kl_grouped_gemm_mma(
+            _ptr(a), ctypes.c_longlong(a.stride(0)), ctypes.c_longlong(a_group_stride), _ptr(w), ctypes.c_longlong(NW * K), _ptr(out),
+            ctypes.c_longlong(out.stride(0)), ctypes.c_longlong(out_group_stride), G, M, N, K, _ptr(row_gate),
+            ctypes.c_longlong(0 if row_gate is None else row_gate.stride(0)), _stream()), "grouped_gemm_mma")
+        return
     _check(lib("grouped_gemm").kl_grouped_gemm(
         _ptr(a), ctypes.c_longlong(a.stride(0)), ctypes.c_longlong(a_group_stride), _ptr(a_rows), _ptr(w), ctypes.c_longlong(NW * K),
         _ptr(out), ctypes.c_longlong(out.stride(0)), ctypes.c_longlong(out_group_stride), _ptr(tile_group), tiles, tile_rows, G, M, N, K,
@@ -565,6 +576,16 @@ def latent_prepare(proj: torch.Tensor, q_col: int, kv_col: Optional[int], norm_w
         n_tokens, heads, dim, rot_dim, kv_rank, dtype_code(proj.dtype), _stream()), "latent_prepare")
 
 
+def latent_decode_splits(n_seqs: int, heads: int, context_class: int) -> int:
+    """Into how many runs a decode step cuts every sequence's pages: by the step's class of context length (never by the
+    length itself: a captured step is replayed while the context grows inside its class), at least two pages a run, and
+    no more CTAs than two for every multiprocessor."""
+    head_blocks = -(-heads // 64)
+    pages = 16 << max(0, int(context_class))                   # the most pages of the class
+    room = max(1, (2 * sm_count()) // max(1, n_seqs * head_blocks))
+    return max(1, min(pages // 2, room, 32))
+
+
 LATENT_KERNEL = "mma"           # "simt": the plain kernel also for bfloat16 (for comparisons)
 
 
@@ -582,10 +603,15 @@ def latent_attention(qfull: torch.Tensor, out: torch.Tensor, cache: torch.Tensor
               and qfull.shape[0] >= n and qfull.shape[1] == heads * key_dim and out.shape[0] >= n and out.shape[1] == heads * value_dim
               and tuple(cache.shape[1:]) == (1, PAGE, key_dim), "latent_attention: layouts")
         _need(sink is None or (sink.dtype == torch.float32 and sink.is_contiguous() and sink.numel() == heads), "latent_attention: sink")
+        splits, part = 1, None
+        if step.is_decode and n == step.n_seqs:
+            splits = latent_decode_splits(step.n_seqs, heads, getattr(step, "context_class", 0))
+            if splits > 1:
+                part = torch.empty(n * heads * splits * (value_dim + 2), dtype=torch.float32, device=qfull.device)
         _check(lib("attention_latent").kl_latent_attention_mma(
             _ptr(qfull), _ptr(out), _ptr(cache), _ptr(block_table), block_table.shape[1], _ptr(step.cu_tokens), _ptr(step.seq_slots),
             _ptr(step.seq_starts), _ptr(step.seq_new), step.n_seqs, step.max_new, _ptr(sink), heads, key_dim, value_dim,
-            ctypes.c_float(scale), _stream()), "latent_attention_mma")
+            ctypes.c_float(scale), splits, _ptr(part), n, _stream()), "latent_attention_mma", 2 if splits > 1 else 1)
         return
     attention_simt(qfull, heads * key_dim, out, cache, cache, block_table, step.positions, step.token_slot, step.n_tokens,
                    heads, 1, key_dim, scale, 0, value_dim=value_dim, sink=sink)

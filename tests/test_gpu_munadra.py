@@ -107,6 +107,13 @@ def test_grouped_product_batched_and_routed(dtype):
         ops.grouped_gemm(a.to(dev), w.to(dev), out, a_group_stride=20, out_group_stride=9, rows=37, tile_rows=tile, row_gate=gate.to(dev))
         got = out.cpu().double().reshape(37, 5, 9)
         assert torch.allclose(got[..., :7], want * torch.sigmoid(gate.double())[..., None], atol=tol, rtol=tol)
+    # batched with 16-byte aligned slices and many rows (bfloat16: the tensor-core form): 3 groups read 40 of every 48 columns
+    a, w, gate = rnd(150, 3 * 48).to(dt), (rnd(3, 70, 40) / 4).to(dt), rnd(150, 3).to(dt)
+    out = torch.zeros(150, 3 * 72, dtype=dt, device=dev)
+    ops.grouped_gemm(a.to(dev), w.to(dev), out, a_group_stride=48, out_group_stride=72, rows=150, row_gate=gate.to(dev))
+    want = torch.einsum("tgk,gnk->tgn", a.double().reshape(150, 3, 48)[..., :40], w.double()) * torch.sigmoid(gate.double())[..., None]
+    got = out.cpu().double().reshape(150, 3, 72)
+    assert torch.allclose(got[..., :70], want, atol=tol * 2, rtol=tol) and float(got[..., 70:].abs().max()) == 0.0
     # routed: 50 tokens choose 2 of 6 groups (one group gets nobody)
     x, wgu, choice = rnd(50, 24).to(dt), (rnd(6, 2 * 10, 24) / 4).to(dt), torch.randint(0, 5, (50, 2), generator=g).int()
     for tile in (16, 64):
@@ -214,6 +221,7 @@ def test_latent_attention_on_the_tensor_cores(H, Dk, Dv):
         step = StepContext(n_tokens=n, n_seqs=3, token_ids=pos, positions=pos, token_slot=tslot, seq_slots=i32([0, 1, 2]), seq_starts=i32(starts),
                            seq_new=i32(news), cu_tokens=i32(cu), is_decode=max(news) == 1, max_new=max(news), max_context=max(a + b for a, b in zip(starts, news)),
                            host_slots=[0, 1, 2], host_starts=starts, host_new=news)
+        step.context_class = 1 if max(news) == 1 and H == 6 else 0           # a decode step: another number of pieces
         for sk in (None, sink):
             want = torch.empty(n, H * Dv, dtype=torch.bfloat16, device=dev)
             got = torch.full_like(want, 9.0)
