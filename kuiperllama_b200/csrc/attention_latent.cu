@@ -57,13 +57,13 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, 
                             const int* __restrict__ block_table, int blocks_per_seq, const int* __restrict__ cu_tokens,
                             const int* __restrict__ seq_slots, const int* __restrict__ seq_starts, const int* __restrict__ seq_new,
                             const float* __restrict__ sink, int H, int HB, int TT, int Dk, int Dv, float scale_log2,
-                            int splits, float* __restrict__ part) {
+                            int splits, float* __restrict__ part, int stages) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(16) uint8_t smem_raw[];
     const int ld = Dk + 8;                                          // elements between rows of shared memory
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                   // [64][ld]
-    bf16* Ks = Qs + (size_t)LA_ROWS * ld;                           // [2][64][ld]
+    bf16* Ks = Qs + (size_t)LA_ROWS * ld;                           // [stages][64][ld]
 
     const int s = blockIdx.z, n_new = seq_new[s], t0 = blockIdx.x * TT, h0 = (blockIdx.y / splits) * HB, piece = blockIdx.y % splits;
     const int slot = seq_slots[s];
@@ -116,10 +116,18 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, 
     const int nv = Dv / 8;                                          // value tiles in use (uniform)
 
     for (int j = first_page; j <= last_page; ++j) {
-        const int buf = (j - first_page) & 1;
-        if (j < last_page) load_page(j + 1, buf ^ 1);
-        cp_async_commit();
-        cp_async_wait<1>();
+        // two buffers: the next page is on its way while this one is worked on.  One buffer (prompts: two CTAs then fit a
+        // multiprocessor and overlap each other's loads, softmax and products): the page is fetched here.
+        const int buf = stages == 2 ? (j - first_page) & 1 : 0;
+        if (stages == 2) {
+            if (j < last_page) load_page(j + 1, buf ^ 1);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            if (j > first_page) load_page(j, 0);
+            cp_async_commit();
+            cp_async_wait<0>();
+        }
         __syncthreads();
         const bf16* K = Ks + (size_t)buf * LA_ROWS * ld;
         // S = Q K^T: 16 rows x 64 keys per warp
@@ -254,6 +262,16 @@ latent_attention_merge_kernel(const float* __restrict__ part, int splits, const 
     }
 }
 
+// KL_LATENT_BUFFERS=2 in the environment keeps two page buffers for prompts too (for comparisons).
+static bool latent_two_buffers() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("KL_LATENT_BUFFERS");
+        v = (e != nullptr && e[0] == '2') ? 1 : 0;
+    }
+    return v != 0;
+}
+
 }  // namespace kl
 
 using namespace kl;
@@ -273,7 +291,10 @@ KL_API int kl_latent_attention_mma(const void* q, void* out, const void* cache, 
     const int HB = H < LA_ROWS ? H : LA_ROWS, TT = LA_ROWS / HB;
     const dim3 grid((max_new + TT - 1) / TT, ((H + HB - 1) / HB) * splits, n_seqs);
     if (grid.y > 65535 || grid.z > 65535) return KL_ERR_BAD_SIZE;
-    const size_t smem = (size_t)3 * LA_ROWS * (Dk + 8) * sizeof(bf16);
+    // prompts: one page buffer where that lets two CTAs share a multiprocessor; decode steps (a chain of pages per CTA): two
+    const size_t one = (size_t)LA_ROWS * (Dk + 8) * sizeof(bf16);
+    const int stages = (max_new > 1 && 2 * (2 * one + 1024) <= 220 * 1024 && !latent_two_buffers()) ? 1 : 2;
+    const size_t smem = (size_t)(1 + stages) * one;
     if (smem > 220 * 1024) return KL_ERR_BAD_SIZE;
     const float scale_log2 = scale * 1.4426950408889634f;
 #define KL_LA(NVT)                                                                                                            \
@@ -285,7 +306,7 @@ KL_API int kl_latent_attention_mma(const void* q, void* out, const void* cache, 
         }                                                                                                                     \
         launch_kernel(latent_attention_mma_kernel<NVT>, grid, LA_THREADS, smem, stream, (const bf16*)q, (bf16*)out,           \
                       (const bf16*)cache, block_table, blocks_per_seq, cu_tokens, seq_slots, seq_starts, seq_new, sink, H, HB, TT, \
-                      Dk, Dv, scale_log2, splits, part);                                                                      \
+                      Dk, Dv, scale_log2, splits, part, stages);                                                              \
     } while (0)
     if (Dv <= 64) KL_LA(8);
     else if (Dv <= 128) KL_LA(16);
