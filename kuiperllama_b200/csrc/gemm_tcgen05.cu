@@ -202,15 +202,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (elect_one()) {
             int issued = 0;                                   // k blocks requested so far, over all tiles
             bool ok = true;
-            if (!WEIGHT_ROWS && args.tile_group != nullptr) pdl_wait();      // the list of groups is written by a kernel ahead
+            if (args.tile_group != nullptr) pdl_wait();       // the list of groups is written by a kernel ahead
             for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
                 int tile_a, tile_b;
                 tile_at(t, tile_a, tile_b);
-                int b_row = tile_b * BN;                      // first row of the B operand's tile
-                if (!WEIGHT_ROWS && args.tile_group != nullptr) {
-                    const int g = args.tile_group[tile_a];
+                int a_row = tile_a * TC_BM, b_row = tile_b * BN;      // first rows of the operands' tiles
+                if (args.tile_group != nullptr) {
+                    // the group's weights: the B operand's rows (tokens as tile rows) or the A operand's (weights as tile rows)
+                    const int g = args.tile_group[WEIGHT_ROWS ? tile_b : tile_a];
                     if (g < 0) continue;
-                    b_row += g * args.group_rows;
+                    if constexpr (WEIGHT_ROWS) a_row += g * args.group_rows;
+                    else b_row += g * args.group_rows;
                 }
                 int first = 0;
                 if (issued == 0) {
@@ -219,13 +221,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const int pre = min(nkb, STAGES);
                     for (int i = 0; i < pre; ++i) {
                         mbar_expect_tx(&full[i], A_BYTES + B_BYTES);
-                        if constexpr (WEIGHT_ROWS) tma_load_2d(tiles_a + i * A_BYTES, &map_a, &full[i], (kb0 + i) * TC_BK, tile_a * TC_BM);
+                        if constexpr (WEIGHT_ROWS) tma_load_2d(tiles_a + i * A_BYTES, &map_a, &full[i], (kb0 + i) * TC_BK, a_row);
                         else tma_load_2d(tiles_b + i * B_BYTES, &map_b, &full[i], (kb0 + i) * TC_BK, b_row);
                     }
                     pdl_wait();
                     for (int i = 0; i < pre; ++i) {
-                        if constexpr (WEIGHT_ROWS) tma_load_2d(tiles_b + i * B_BYTES, &map_b, &full[i], (kb0 + i) * TC_BK, tile_b * BN);
-                        else tma_load_2d(tiles_a + i * A_BYTES, &map_a, &full[i], (kb0 + i) * TC_BK, tile_a * TC_BM);
+                        if constexpr (WEIGHT_ROWS) tma_load_2d(tiles_b + i * B_BYTES, &map_b, &full[i], (kb0 + i) * TC_BK, b_row);
+                        else tma_load_2d(tiles_a + i * A_BYTES, &map_a, &full[i], (kb0 + i) * TC_BK, a_row);
                     }
                     issued = first = pre;
                 }
@@ -233,7 +235,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const int s = issued % STAGES;
                     if (issued >= STAGES && !mbar_wait(&empty[s], ((issued / STAGES) - 1) & 1, abort_flag, args.status, 1)) { ok = false; break; }
                     mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
-                    tma_load_2d(tiles_a + s * A_BYTES, &map_a, &full[s], (kb0 + i) * TC_BK, tile_a * TC_BM);
+                    tma_load_2d(tiles_a + s * A_BYTES, &map_a, &full[s], (kb0 + i) * TC_BK, a_row);
                     tma_load_2d(tiles_b + s * B_BYTES, &map_b, &full[s], (kb0 + i) * TC_BK, b_row);
                     ++issued;
                 }
@@ -256,10 +258,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             bool ok = true;
             int it = 0, lt = 0;                               // k blocks consumed, tiles done (both over all tiles)
             for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++lt) {
-                if (!WEIGHT_ROWS && args.tile_group != nullptr) {
+                if (args.tile_group != nullptr) {
                     int tile_a, tile_b;
                     tile_at(t, tile_a, tile_b);
-                    if (args.tile_group[tile_a] < 0) { --lt; continue; }      // a skipped tile takes no accumulator
+                    if (args.tile_group[WEIGHT_ROWS ? tile_b : tile_a] < 0) { --lt; continue; }      // a skipped tile takes no accumulator
                 }
                 const int buf = lt & 1, use = lt >> 1;
                 if (use > 0) {                                // the epilogue must have read this accumulator out
@@ -309,7 +311,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++lt) {
         int tile_a, tile_b;
         tile_at(t, tile_a, tile_b);
-        if (!WEIGHT_ROWS && args.tile_group != nullptr && args.tile_group[tile_a] < 0) { --lt; continue; }
+        if (args.tile_group != nullptr && args.tile_group[WEIGHT_ROWS ? tile_b : tile_a] < 0) { --lt; continue; }
         const int buf = lt & 1;
         const bool ok = mbar_wait(&acc_full[buf], (lt >> 1) & 1, abort_flag, args.status, 3) && !*abort_flag;
         tc_fence_after();
@@ -355,7 +357,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                 const int m = c + j, token = tile_b * BN + m;
                                 if (token < args.rows_b)
                                     outb[(size_t)token * args.ld_out + feature] =
-                                        __float2bfloat16_rn(silu_mul(__uint_as_float(r[j]) * inv_rms[m], xch[m * 64 + f]));
+                                        __float2bfloat16_rn(gated_mul(args, __uint_as_float(r[j]) * inv_rms[m], xch[m * 64 + f]));
                             }
                         }
                     }
@@ -767,6 +769,33 @@ KL_API int kl_gemm_tcgen05_grouped(const void* a, long long lda, const void* w, 
     if (sms <= 0) return KL_ERR_SETUP;
     dim3 grid(min(tiles_m * tiles_n, sms), 1, 1);
     return launch<256, 4, false>(ma, mb, args, grid, stream);
+}
+
+// The grouped product for few rows per group: weights as tile rows.  The list's tiles are 16 places (tile_group[list tile]:
+// the group, -1: skipped; a holds the list's rows, M = tiles * 16, gathered); one CTA per (128 weight rows, list tile), so
+// every chosen group's weights stream once through the TMA ring.  gated as in kl_gemm_tcgen05_grouped.
+KL_API int kl_gemm_tcgen05_grouped_skinny(const void* a, long long lda, const void* w, long long ldw, void* out, long long ldo,
+                                          int M, int n_rows, int K, int groups, const int* tile_group, int gated, float limit,
+                                          float alpha, float shift, int* status, cudaStream_t stream) {
+    if (M <= 0 || n_rows <= 0 || groups <= 0) return KL_OK;
+    if (M % 16 || tile_group == nullptr || (gated && n_rows % 128)) return KL_ERR_BAD_SIZE;
+    if (!aligned_operand(a, lda, K) || !aligned_operand(w, ldw, K)) return KL_ERR_BAD_ALIGN;
+    if ((long long)groups * n_rows > 0x7fffffffLL) return KL_ERR_BAD_SIZE;
+    CUtensorMap ma, mb;
+    int rc;
+    if ((rc = make_map(&ma, w, groups * n_rows, K, ldw, TC_BM)) != KL_OK) return rc;
+    if ((rc = make_map(&mb, a, M, K, lda, 16)) != KL_OK) return rc;
+    const int list_tiles = M / 16;
+    GemmArgs args{out, ldo, 0, n_rows, M, (K + TC_BK - 1) / TC_BK, 0, status, list_tiles, 0, gated};
+    args.K = K;
+    args.tile_group = tile_group;
+    args.group_rows = n_rows;
+    args.act_custom = gated;
+    args.act_limit = limit; args.act_alpha = alpha; args.act_shift = shift;
+    const long long ctas = (long long)((n_rows + TC_BM - 1) / TC_BM) * list_tiles;
+    if (ctas > 0x7fffffffLL) return KL_ERR_BAD_SIZE;
+    dim3 grid((unsigned)ctas, 1, 1);
+    return launch<16, 6, true>(ma, mb, args, grid, stream);
 }
 
 // Few tokens (M <= 512): weights as tile rows (beyond 64 tokens: up to four tiles of 128 tokens per

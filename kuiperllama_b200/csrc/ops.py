@@ -537,6 +537,25 @@ def gemm_tcgen05_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, ti
         _status_ptr(a.device), _stream()), "gemm_tcgen05_grouped")
 
 
+def gemm_tcgen05_grouped_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_group: torch.Tensor,
+                                gated: Optional[tuple] = None) -> None:
+    """The grouped product for few rows per group on the tensor cores, weights as tile rows: ``a`` holds the list's rows (tiles of
+    16 places, ``tile_group`` [places / 16], -1: skipped); every chosen group's weights stream once through the TMA ring.
+    Operands as for ``gemm_tcgen05_grouped``."""
+    _cuda(a, w, out, tile_group)
+    _i32(tile_group, "tile_group")
+    G, R, K = w.shape
+    M = tile_group.numel() * 16
+    _need(w.is_contiguous() and a.shape[1] == K and a.shape[0] >= M and out.shape[0] >= M and out.dtype == torch.bfloat16
+          and out.shape[1] == (R // 2 if gated is not None else R), "gemm_tcgen05_grouped_skinny: shapes")
+    _need(_tc_ok(a, w[0], out) and (gated is None or R % 128 == 0), "gemm_tcgen05_grouped_skinny: bfloat16 operands with 16-byte aligned rows")
+    lim, alpha, shift = gated if gated is not None else (0.0, 1.0, 0.0)
+    _check(lib("gemm_tcgen05").kl_gemm_tcgen05_grouped_skinny(
+        _ptr(a), ctypes.c_longlong(a.stride(0)), _ptr(w), ctypes.c_longlong(K), _ptr(out), ctypes.c_longlong(out.stride(0)), M, R, K, G,
+        _ptr(tile_group), int(gated is not None), ctypes.c_float(lim), ctypes.c_float(alpha), ctypes.c_float(shift),
+        _status_ptr(a.device), _stream()), "gemm_tcgen05_grouped_skinny")
+
+
 def moe_combine(results: torch.Tensor, pair_pos: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
     """out[t] = sum_k weight[t, k] * results[pair_pos[t * top + k]] (float32 [tokens, hidden]), in the order of k."""
     _cuda(results, pair_pos, weight, out)

@@ -34,6 +34,7 @@ class MoEFeedForward(FeedForward):
     # experts of 2,048 (ms per decode step of 16 layers): 64 sequences (16 rows per expert) 3.15 on the tensor cores against 9.5 on
     # the warp-per-rows form; 8 sequences (2 rows per expert) 2.93 on the latter.
     TENSOR_CORE_ROWS_PER_EXPERT = 8
+    SKINNY = __import__("os").environ.get("KL_MOE_SKINNY", "tcgen05")     # "gemv": the warp-per-rows form (for comparisons)
 
     @classmethod
     def manifest(cls, spec: PartSpec, prefix: str) -> Dict[str, TensorDecl]:
@@ -85,7 +86,12 @@ class MoEFeedForward(FeedForward):
             cap = list_rows.numel()
             act = torch.empty((cap, self.ff), dtype=dt, device=dev)
             res = torch.empty((cap, self.hidden), dtype=dt, device=dev)
-            if tile == 16 and dt == torch.bfloat16 and self.hidden % 8 == 0 and self.ff % 8 == 0 and x.stride(0) % 8 == 0:
+            if tile == 16 and self.tensor_cores and self.SKINNY == "tcgen05" and x.stride(0) % 8 == 0:
+                # a few rows per expert: the chosen experts' weights stream once through the tensor-core kernel's TMA ring
+                rows = ops.moe_gather(x, list_rows)
+                ops.gemm_tcgen05_grouped_skinny(rows, self.gate_up, act, tile_group, gated=self.activation)
+                ops.gemm_tcgen05_grouped_skinny(act, self.down, res, tile_group)
+            elif tile == 16 and dt == torch.bfloat16 and self.hidden % 8 == 0 and self.ff % 8 == 0 and x.stride(0) % 8 == 0:
                 # a few rows per expert: bound by reading the chosen experts' weights once
                 ops.grouped_gemv(x, self.gate_up, act, list_rows, tile_group, tile, gated=self.activation, interleaved=self.tensor_cores)
                 ops.grouped_gemv(act, self.down, res, None, tile_group, tile, live_rows=list_rows)

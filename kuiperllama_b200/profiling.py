@@ -32,7 +32,7 @@ KERNEL_ENTRY_POINTS = ("embedding", "add_rmsnorm", "swiglu", "rope_kv_write", "a
                        "sample_rows", "token_logprob", "logit_transform", "gemm_tcgen05", "gemm_skinny_stream",
                        "gemm_skinny_partials", "gemm_skinny", "attention_decode", "attention_mma", "attention_tcgen05",
                        "attention_decode_fused", "norm_chain", "head_rmsnorm_gate", "activation", "sigmoid_gate", "mingru_scan",
-                       "gated_delta_rule", "grouped_gemm", "grouped_gemv", "gemm_tcgen05_grouped", "moe_route", "moe_plan", "moe_gather", "moe_combine",
+                       "gated_delta_rule", "grouped_gemm", "grouped_gemv", "gemm_tcgen05_grouped", "gemm_tcgen05_grouped_skinny", "moe_route", "moe_plan", "moe_gather", "moe_combine",
                        "latent_prepare", "latent_attention", "causal_conv", "rglru_gate", "linear_scan")
 
 

@@ -196,6 +196,15 @@ def test_grouped_product_for_few_rows():
             live = (list_rows >= 0)
             assert torch.allclose(got2.float()[live], want2.float()[live], atol=2e-2, rtol=2e-2)
             assert float(got2.float()[~live].abs().max()) == 0.0, "padding places are left alone"
+            if inter and K % 8 == 0:
+                # the same on the tensor cores, weights as tile rows
+                rows = ops.moe_gather(x, list_rows)
+                got3, got4 = torch.zeros_like(want), torch.zeros_like(want2)
+                ops.gemm_tcgen05_grouped_skinny(rows, w, got3, tile_group, gated=gated)
+                ops.gemm_tcgen05_grouped_skinny(want, down, got4, tile_group)
+                ops.check_status(torch.device(dev))
+                assert torch.allclose(got3.float()[live], want.float()[live], atol=2e-2, rtol=2e-2)
+                assert torch.allclose(got4.float()[live], want2.float()[live], atol=2e-2, rtol=2e-2)
 
 
 @pytest.mark.parametrize("H, Dk, Dv", [(6, 96, 64), (32, 288, 256), (80, 48, 16), (3, 160, 144)])
