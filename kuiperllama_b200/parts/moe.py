@@ -24,7 +24,10 @@ class MoEFeedForward(FeedForward):
     Routing stays on the device (``ops.moe_route`` / ``moe_plan``): the (token, choice) pairs are sorted by
     expert into a list padded to whole tiles, one grouped product makes gate, up and the activation for
     the whole list, one more the down projection, and ``moe_combine`` adds each token's results in the
-    order of its choices in 32 bits.  The result is handed on as one float32 piece.
+    order of its choices in 32 bits.  The result is handed on as one float32 piece.  The grouped products run on the
+    tensor cores where the sizes allow (bfloat16, expert size % 64, hidden size % 8): tokens as tile rows from
+    ``TENSOR_CORE_ROWS_PER_EXPERT`` rows per expert on, weights as tile rows below (a decode step); on FMA kernels
+    otherwise (float32, odd sizes).
 
     Spec: ``hidden_size``, ``experts``, ``top``, ``expert_size``, ``limit``, ``alpha``, ``shift``, ``renormalise``,
     ``names``: router and, with ``{e}`` for the expert's number, gate, up, down.  KuiperLLama's only feed-forward is
@@ -32,7 +35,7 @@ class MoEFeedForward(FeedForward):
 
     # Mean rows per expert from which the list is cut into tiles of 128 for the tensor cores.  Measured at width 2,048 with 16
     # experts of 2,048 (ms per decode step of 16 layers): 64 sequences (16 rows per expert) 3.15 on the tensor cores against 9.5 on
-    # the warp-per-rows form; 8 sequences (2 rows per expert) 2.93 on the latter.
+    # the warp-per-rows form; 8 sequences (2 rows per expert) 2.08 with weights as tile rows, 2.76 on the warp-per-rows form.
     TENSOR_CORE_ROWS_PER_EXPERT = 8
     SKINNY = __import__("os").environ.get("KL_MOE_SKINNY", "tcgen05")     # "gemv": the warp-per-rows form (for comparisons)
 
