@@ -163,7 +163,7 @@ def oracle_logits(folder: str, toks: Sequence[int]) -> torch.Tensor:
 OBSERVED: Dict[tuple, float] = {}      # (dtype, what) -> the largest row error seen, for the report at the end of a run
 
 
-def assert_logits(got: torch.Tensor, ref: torch.Tensor, dtype: str, what: str) -> None:
+def assert_logits(got: torch.Tensor, ref: torch.Tensor, dtype: str, what: str, routed_layers: int = 0) -> None:
     """Per row, the difference with its mean taken off, root mean square over the vocabulary, relative to the
     reference row's spread.  float32 (the sharp test: only the order of sums differs): 1e-4 for every row.
     bfloat16 is judged by shares, for two reasons measured on the "mixed" configuration (stream against
@@ -172,7 +172,8 @@ def assert_logits(got: torch.Tensor, ref: torch.Tensor, dtype: str, what: str) -
     stream's size (the median row is off by 0.3 % after one layer and 6 % after six), and a router whose
     scores around the cut are close picks another expert than float64 does (a third of the rows in the
     last of three routed layers), which moves that row by up to its whole spread.  The same rows do so
-    under every cut and batch.  Limits: half of the rows within 10 %, nine in ten within 50 %."""
+    under every cut and batch.  Limits: half of the rows within 10 %, nine in ten within 50 %; for models of which
+    three or more layers are routed (``routed_layers``; the random configurations) 25 % and 75 %."""
     got, ref = got.detach().double().cpu(), ref.detach().double().cpu()
     assert got.shape == ref.shape, f"{what}: shape {tuple(got.shape)} vs {tuple(ref.shape)}"
     assert torch.isfinite(got).all(), f"{what}: non-finite logits"
@@ -189,5 +190,6 @@ def assert_logits(got: torch.Tensor, ref: torch.Tensor, dtype: str, what: str) -
     if err.numel() < 20:                # a handful of rows: one other choice of an expert early on colours them all
         assert half <= 3e-1, f"{what}: half of the {err.numel()} rows are off by more than {half:.3e} of their spread (limit 3e-01)"
         return
-    assert half <= 1e-1, f"{what}: half of the rows are off by more than {half:.3e} of their spread (limit 1e-01)"
-    assert most <= 5e-1, f"{what}: a tenth of the rows is off by more than {most:.3e} of their spread (limit 5e-01)"
+    lim_half, lim_most = (2.5e-1, 7.5e-1) if routed_layers >= 3 else (1e-1, 5e-1)
+    assert half <= lim_half, f"{what}: half of the rows are off by more than {half:.3e} of their spread (limit {lim_half:.0e})"
+    assert most <= lim_most, f"{what}: a tenth of the rows is off by more than {most:.3e} of their spread (limit {lim_most:.0e})"
