@@ -75,6 +75,9 @@ class AttentionMixer(Mixer):
         self.o = Linear(tensors[prefix + n["o"]], runtime)
         rot = position.rotary() if position is not None else None
         self.inv_freq, self.rotary_dim = rot if rot is not None else (None, 0)
+        if position is not None and (getattr(position, "pairing", "half") != "half" or getattr(position, "magnitude", 1.0) != 1.0):
+            raise ValueError("this mixer's kernels rotate half-split pairs with unit magnitude; interleaved pairs and a factor on "
+                             "cos and sin are what the latent-attention mixer's kernel does")
 
     def kv_request(self) -> Optional[KVRequest]:
         return KVRequest(kv_heads=self.KV, head_dim=self.hd, kind="full", window=self.window)

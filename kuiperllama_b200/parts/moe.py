@@ -1,6 +1,7 @@
 """A mixture of experts as a feed-forward: a router, a grouped product per projection, a weighted sum."""
 from __future__ import annotations
 
+import os
 from typing import Dict
 
 import torch
@@ -37,7 +38,7 @@ class MoEFeedForward(FeedForward):
     # experts of 2,048 (ms per decode step of 16 layers): 64 sequences (16 rows per expert) 3.15 on the tensor cores against 9.5 on
     # the warp-per-rows form; 8 sequences (2 rows per expert) 2.08 with weights as tile rows, 2.76 on the warp-per-rows form.
     TENSOR_CORE_ROWS_PER_EXPERT = 8
-    SKINNY = __import__("os").environ.get("KL_MOE_SKINNY", "tcgen05")     # "gemv": the warp-per-rows form (for comparisons)
+    SKINNY = os.environ.get("KL_MOE_SKINNY", "tcgen05")     # "gemv": the warp-per-rows form (for comparisons)
 
     @classmethod
     def manifest(cls, spec: PartSpec, prefix: str) -> Dict[str, TensorDecl]:
